@@ -1,0 +1,9 @@
+"""Typed configurations, the architecture registry and the model plan."""
+from .plan import LayerSpec, ModelPlan, PartSpec, ScheduleEntry, default_schedule
+from .registry import (ConfigError, config_from_dict, load_config, register_architecture,
+                       registered_architectures, resolve_architecture)
+from .qwen2 import Qwen2Config
+
+__all__ = ["LayerSpec", "ModelPlan", "PartSpec", "ScheduleEntry", "default_schedule", "ConfigError",
+           "config_from_dict", "load_config", "register_architecture", "registered_architectures",
+           "resolve_architecture", "Qwen2Config"]

@@ -1,0 +1,74 @@
+// Shared helpers of the sm_100a kernels: dtype conversion, warp/block reductions,
+// argument checks.  Every exported function returns 0 on success, a positive
+// cudaError_t, or a negative IFX_E_* code for arguments it refuses.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define IFX_DT_F32 0
+#define IFX_DT_BF16 1
+
+#define IFX_E_BADARG (-1)      // a size or option the kernel does not take
+#define IFX_E_DTYPE (-2)       // unknown dtype code
+#define IFX_E_ALIGN (-3)       // a pointer or stride that breaks an alignment rule
+#define IFX_E_TOOBIG (-4)      // beyond a stated maximum
+
+#define IFX_CHECK_LAUNCH()                         \
+  do {                                             \
+    cudaError_t e__ = cudaGetLastError();          \
+    if (e__ != cudaSuccess) return (int)e__;       \
+  } while (0)
+
+namespace ifx {
+
+__device__ __forceinline__ float to_f32(float v) { return v; }
+__device__ __forceinline__ float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) {
+  return __float2bfloat16_rn(v);
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Sum over a block of up to 1024 threads; every thread gets the result.  The order
+// of the additions depends only on the block size, so a row's result does not
+// depend on which other rows are in the launch.
+__device__ __forceinline__ float block_sum(float v, float* scratch /* >= 32 floats */) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int nwarps = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();                       // scratch may still be read from a previous call
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  float r = (lane < nwarps) ? scratch[lane] : 0.0f;
+  r = warp_sum(r);
+  return r;
+}
+
+__device__ __forceinline__ float block_max(float v, float* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int nwarps = (blockDim.x + 31) >> 5;
+  v = warp_max(v);
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  float r = (lane < nwarps) ? scratch[lane] : -INFINITY;
+  r = warp_max(r);
+  return r;
+}
+
+}  // namespace ifx

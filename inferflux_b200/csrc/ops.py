@@ -1,0 +1,223 @@
+"""The kernel table of the product path: every operation of a step as a call into
+the hand-written sm_100a library (plus cuBLAS for the bfloat16 matrix products,
+where the reference uses it too).
+
+There is no CPU path and no library model code here: making a `CudaKernels`
+without a CUDA device, or without being able to build or load the library, raises.
+Tensors are passed as raw device pointers on torch's current stream.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from .build import BuildError, load_library
+
+_DT = {torch.float32: 0, torch.bfloat16: 1}
+
+_ERRORS = {-1: "a size or option the kernel does not take", -2: "unknown dtype",
+           -3: "a pointer or stride breaks an alignment rule", -4: "a size beyond the kernel's stated maximum"}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return ctypes.c_void_p(0 if t is None else t.data_ptr())
+
+
+def _stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _check(rc: int, what: str) -> None:
+    if rc == 0:
+        return
+    if rc < 0:
+        raise KernelError(f"{what}: refused ({_ERRORS.get(rc, rc)})")
+    if rc >= 1000:
+        raise KernelError(f"{what}: cuBLAS status {rc - 1000}")
+    raise KernelError(f"{what}: CUDA error {rc}")
+
+
+def _need(cond: bool, msg: str) -> None:
+    if not cond:
+        raise KernelError(msg)
+
+
+class CudaKernels:
+    """Kernel table on one CUDA device."""
+
+    name = "cuda-sm100a"
+
+    def __init__(self, device="cuda"):
+        if not torch.cuda.is_available():
+            raise BuildError("no CUDA device: the engine has no CPU path")
+        self.device = torch.device(device)
+        self.lib = load_library()
+        for fn in ("ifx_embed", "ifx_rmsnorm", "ifx_silu_mul", "ifx_residual_add", "ifx_gather_rows",
+                   "ifx_scatter_i32", "ifx_rope_append", "ifx_attention_generic", "ifx_gemm_generic",
+                   "ifx_gemm_cublas_bf16", "ifx_cublas_init", "ifx_argmax", "ifx_penalties", "ifx_logit_bias",
+                   "ifx_sample"):
+            getattr(self.lib, fn).restype = ctypes.c_int
+        with torch.cuda.device(self.device):
+            _check(self.lib.ifx_cublas_init(), "cublas init")
+        self.launches = 0            # kernels of this library launched so far (library GEMMs included)
+
+    # ------------------------------------------------------------- elementwise
+    def embed(self, table, token_ids, vocab):
+        T, H = token_ids.numel(), table.shape[1]
+        out = torch.empty((T, H), dtype=torch.float32, device=table.device)
+        _check(self.lib.ifx_embed(_ptr(table), _ptr(token_ids), _ptr(out), T, H, int(vocab), _DT[table.dtype],
+                                  _stream()), "embed")
+        self.launches += 1
+        return out
+
+    def rmsnorm(self, x, w, eps, out_dtype):
+        _need(x.dtype == torch.float32 and w.dtype == torch.float32, "rmsnorm: x and w must be float32")
+        T, H = x.shape
+        out = torch.empty((T, H), dtype=out_dtype, device=x.device)
+        _check(self.lib.ifx_rmsnorm(_ptr(x), _ptr(None), _ptr(w), _ptr(out), T, H, ctypes.c_float(eps),
+                                    _DT[out_dtype], _stream()), "rmsnorm")
+        self.launches += 1
+        return out
+
+    def add_rmsnorm(self, x, delta, w, eps, out_dtype):
+        _need(x.dtype == torch.float32 and w.dtype == torch.float32, "add_rmsnorm: x and w must be float32")
+        _need(delta.dtype == out_dtype and delta.shape == x.shape, "add_rmsnorm: delta must match x and the dtype")
+        T, H = x.shape
+        out = torch.empty((T, H), dtype=out_dtype, device=x.device)
+        _check(self.lib.ifx_rmsnorm(_ptr(x), _ptr(delta), _ptr(w), _ptr(out), T, H, ctypes.c_float(eps),
+                                    _DT[out_dtype], _stream()), "add_rmsnorm")
+        self.launches += 1
+        return out
+
+    def residual_add(self, x, delta):
+        T, H = x.shape
+        _check(self.lib.ifx_residual_add(_ptr(x), _ptr(delta), T, H, _DT[delta.dtype], _stream()), "residual_add")
+        self.launches += 1
+
+    def silu_mul(self, gate_up):
+        T, two_i = gate_up.shape
+        out = torch.empty((T, two_i // 2), dtype=gate_up.dtype, device=gate_up.device)
+        _check(self.lib.ifx_silu_mul(_ptr(gate_up), _ptr(out), T, two_i // 2, _DT[gate_up.dtype], _stream()),
+               "silu_mul")
+        self.launches += 1
+        return out
+
+    def gather_rows(self, x, rows):
+        R, H = rows.numel(), x.shape[1]
+        out = torch.empty((R, H), dtype=torch.float32, device=x.device)
+        _check(self.lib.ifx_gather_rows(_ptr(x), _ptr(rows), _ptr(out), R, H, x.shape[0], _stream()), "gather_rows")
+        self.launches += 1
+        return out
+
+    def scatter_i32(self, table, index, value):
+        n = index.numel()
+        if n:
+            _check(self.lib.ifx_scatter_i32(_ptr(table), _ptr(index), _ptr(value), n, table.numel(), _stream()),
+                   "scatter_i32")
+            self.launches += 1
+
+    # ------------------------------------------------------------------ linear
+    def linear(self, a, w, bias=None, out_dtype=None):
+        """out[T, N] = a[T, K] . w[N, K]^T (+ bias), float32 accumulation."""
+        _need(a.dtype == w.dtype, f"linear: activations are {a.dtype}, weights {w.dtype}")
+        _need(a.is_contiguous() and w.is_contiguous(), "linear: operands must be contiguous")
+        T, K = a.shape
+        N = w.shape[0]
+        _need(w.shape[1] == K, f"linear: inner sizes differ ({K} vs {w.shape[1]})")
+        out_dtype = out_dtype or a.dtype
+        out = torch.empty((T, N), dtype=out_dtype, device=a.device)
+        if T == 0:
+            return out
+        if a.dtype == torch.float32:
+            _need(out_dtype == torch.float32, "linear: a float32 product gives float32")
+            _check(self.lib.ifx_gemm_generic(_ptr(a), _ptr(w), _ptr(bias), _ptr(out), T, N, K, 0, 0, _stream()),
+                   "gemm (float32)")
+            self.launches += 1
+            return out
+        _check(self.lib.ifx_gemm_cublas_bf16(_ptr(a), _ptr(w), _ptr(out), T, N, K, _DT[out_dtype], _stream()),
+               "gemm (bfloat16)")
+        self.launches += 1
+        if bias is not None:
+            out += bias.to(out.dtype)
+        return out
+
+    def linear_generic(self, a, w, bias=None, out_dtype=None):
+        """The CUDA-core product for any dtype (used by tests and as the refusal-free path)."""
+        T, K = a.shape
+        N = w.shape[0]
+        out_dtype = out_dtype or a.dtype
+        out = torch.empty((T, N), dtype=out_dtype, device=a.device)
+        _check(self.lib.ifx_gemm_generic(_ptr(a), _ptr(w), _ptr(bias), _ptr(out), T, N, K, _DT[a.dtype],
+                                         _DT[out_dtype], _stream()), "gemm_generic")
+        self.launches += 1
+        return out
+
+    # --------------------------------------------------------------- attention
+    def rope_append(self, qkv, bias, rotary, nq, nkv, d, ctx, cache):
+        T = qkv.shape[0]
+        _need(qkv.shape[1] == (nq + 2 * nkv) * d, "rope_append: qkv width does not fit the head counts")
+        q_out = torch.empty((T, nq * d), dtype=qkv.dtype, device=qkv.device)
+        write = bool(cache.writes and cache.kv is not None)
+        kv, table = cache.kv, cache.block_table
+        if write:
+            _need(kv.dtype == qkv.dtype, f"rope_append: cache is {kv.dtype}, activations {qkv.dtype}")
+        rot = 0 if rotary is None else int(rotary.rotary_dim)
+        _need(rot <= d, "rope_append: rotary_dim exceeds the head size")
+        _check(self.lib.ifx_rope_append(
+            _ptr(qkv), _ptr(bias), _ptr(None if rotary is None else rotary.inv_freq), rot,
+            int(bool(rotary.interleaved)) if rotary is not None else 0,
+            _ptr(ctx.positions), _ptr(ctx.token_req), _ptr(ctx.req_slot), _ptr(table),
+            0 if table is None else table.shape[1], cache.page_size, 0 if kv is None else kv.shape[0],
+            _ptr(kv), _ptr(q_out), T, nq, nkv, d, int(write), _DT[qkv.dtype], _stream()), "rope_append")
+        self.launches += 1
+        return q_out
+
+    def attention(self, q, nq, nkv, d, window, scale, ctx, cache):
+        T = q.shape[0]
+        kv, table = cache.kv, cache.block_table
+        _need(kv is not None and table is not None, "attention: the mixer has no key/value cache")
+        _need(kv.dtype == q.dtype, f"attention: cache is {kv.dtype}, queries {q.dtype}")
+        _need(d % 8 == 0 and d <= 256, f"attention: head size {d} is not a multiple of 8 up to 256")
+        out = torch.empty((T, nq * d), dtype=q.dtype, device=q.device)
+        _check(self.lib.ifx_attention_generic(
+            _ptr(q), _ptr(kv), _ptr(table), _ptr(ctx.positions), _ptr(ctx.token_req), _ptr(ctx.req_slot),
+            _ptr(out), T, nq, nkv, d, cache.page_size, table.shape[1], kv.shape[0],
+            0 if window is None else int(window), ctypes.c_float(scale), _DT[q.dtype], _stream()), "attention")
+        self.launches += 1
+        return out
+
+    # ---------------------------------------------------------------- sampling
+    def argmax(self, logits):
+        R, V = logits.shape
+        out = torch.empty((R,), dtype=torch.int32, device=logits.device)
+        _check(self.lib.ifx_argmax(_ptr(logits), _ptr(out), R, V, _stream()), "argmax")
+        self.launches += 1
+        return out
+
+    def penalties(self, logits, tokens, counts, rep, freq, pres):
+        R, V = logits.shape
+        _check(self.lib.ifx_penalties(_ptr(logits), _ptr(tokens), _ptr(counts), _ptr(rep), _ptr(freq), _ptr(pres),
+                                      R, tokens.shape[1], V, _stream()), "penalties")
+        self.launches += 1
+
+    def logit_bias(self, logits, rows, tokens, bias):
+        R, V = logits.shape
+        _check(self.lib.ifx_logit_bias(_ptr(logits), _ptr(rows), _ptr(tokens), _ptr(bias), rows.numel(), R, V,
+                                       _stream()), "logit_bias")
+        self.launches += 1
+
+    def sample(self, logits, temperature, top_k, top_p, min_p, seed_lo, seed_hi, step):
+        R, V = logits.shape
+        probs = torch.empty((R, V), dtype=torch.float32, device=logits.device)
+        out = torch.empty((R,), dtype=torch.int32, device=logits.device)
+        _check(self.lib.ifx_sample(_ptr(logits), _ptr(probs), _ptr(temperature), _ptr(top_k), _ptr(top_p),
+                                   _ptr(min_p), _ptr(seed_lo), _ptr(seed_hi), _ptr(step), _ptr(out), R, V,
+                                   _stream()), "sample")
+        self.launches += 1
+        return out

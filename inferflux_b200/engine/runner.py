@@ -1,0 +1,122 @@
+"""The step function: run a batch of (request, its next tokens) through the model,
+from the cache that earlier steps left, and return the logits at the wanted places.
+
+The reference's counterpart is InferfluxCudaExecutor::ExecuteUnifiedBatch
+(runtime/backends/cuda/inferflux_cuda_executor.cpp:3165-3769), which batches the
+single-token rows and then runs each prompt portion in a forward call of its own.
+Here every token of every entry goes through one forward: portions of prompts beside
+single decoded tokens, cut anywhere.  Indices are checked on the host before
+anything is launched (the reference does the same for slots and positions,
+:3234-3253), so no kernel is ever handed an index outside its tables.
+"""
+from __future__ import annotations
+
+from typing import Hashable, List, Optional, Sequence
+
+import torch
+
+from ..cache.manager import CacheManager
+from ..cache.pages import OutOfPages
+from .batch import StepContext, StepEntry
+
+
+class StepError(ValueError):
+    """A batch that cannot be run: bad token id, too long, duplicate request."""
+
+
+class ModelRunner:
+    """A loaded model, its cache and the kernel table: everything `step` needs."""
+
+    def __init__(self, model, kernels, page_size: int = 16, num_pages: int = 256, max_seqs: int = 8,
+                 max_seq_len: Optional[int] = None, cache_dtype: Optional[torch.dtype] = None):
+        self.model = model
+        self.kernels = kernels
+        self.dtype = model.dtype
+        self.device = model.device
+        self.vocab_size = model.plan.vocab_size
+        limit = model.plan.max_positions
+        self.max_seq_len = min(limit, max_seq_len) if max_seq_len else limit
+        self.cache = CacheManager(model.cache_specs(), page_size=page_size, num_pages=num_pages,
+                                  max_seqs=max_seqs, max_seq_len=self.max_seq_len,
+                                  dtype=cache_dtype or model.dtype, device=self.device)
+        self.steps = 0
+        self.tokens_run = 0
+
+    # ---------------------------------------------------------------- requests
+    def add_request(self, rid: Hashable) -> int:
+        return self.cache.add_request(rid)
+
+    def end_request(self, rid: Hashable) -> None:
+        """Give back the pages and the slot of a finished request."""
+        self.cache.free(rid)
+
+    def length(self, rid: Hashable) -> int:
+        return self.cache.length(rid)
+
+    # -------------------------------------------------------------------- step
+    def validate(self, entries: Sequence[StepEntry]) -> None:
+        seen = set()
+        for e in entries:
+            if e.request_id in seen:
+                raise StepError(f"request {e.request_id!r} appears twice in one step")
+            seen.add(e.request_id)
+            if len(e.tokens) == 0:
+                raise StepError(f"request {e.request_id!r}: no tokens")
+            bad = [int(t) for t in e.tokens if not 0 <= int(t) < self.vocab_size]
+            if bad:
+                raise StepError(f"request {e.request_id!r}: token ids {bad[:8]} are outside the vocabulary "
+                                f"of {self.vocab_size}")
+            start = self.cache.length(e.request_id) if e.request_id in self.cache else 0
+            if start + len(e.tokens) > self.max_seq_len:
+                raise StepError(f"request {e.request_id!r}: {start + len(e.tokens)} tokens exceed the longest "
+                                f"sequence of {self.max_seq_len}")
+            for w in e.want:
+                if not 0 <= int(w) < len(e.tokens):
+                    raise StepError(f"request {e.request_id!r}: wanted place {w} is outside its "
+                                    f"{len(e.tokens)} tokens")
+
+    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+        """Run only the tokens given, as one batch.  Returns float32 logits
+        [number of wanted places, vocab] in the order of the entries and of `want`.
+        Raises OutOfPages (nothing taken, nothing run) when the pool cannot hold the step."""
+        entries = list(entries)
+        if not entries:
+            return torch.empty((0, self.vocab_size), dtype=torch.float32, device=self.device)
+        self.validate(entries)
+        cache = self.cache
+        fresh = [e.request_id for e in entries if e.request_id not in cache]
+        if len(fresh) > cache.num_free_slots:
+            raise OutOfPages(f"{len(fresh)} new requests but {cache.num_free_slots} free request slots")
+
+        # ---- can the pool hold the whole step?  Decide before taking anything.
+        need = [0] * len(cache.groups)
+        for e in entries:
+            if e.request_id in cache:
+                per = cache.pages_needed(e.request_id, cache.length(e.request_id) + len(e.tokens))
+            else:
+                per = cache.pages_needed_fresh(len(e.tokens))
+            need = [a + b for a, b in zip(need, per)]
+        free = cache.free_pages()
+        if any(n > f for n, f in zip(need, free)):
+            raise OutOfPages(f"the step needs {need} pages per cache group, free: {free}")
+
+        for rid in fresh:
+            cache.add_request(rid)
+        starts, slots = [], []
+        for e in entries:
+            start = cache.length(e.request_id)
+            cache.reserve(e.request_id, start + len(e.tokens))
+            starts.append(start)
+            slots.append(cache.slot(e.request_id))
+
+        ctx = StepContext.build(self.kernels, self.dtype, self.device, entries, starts, slots,
+                                cache.drain_table_updates())
+        for group, (index, page) in zip(cache.groups, ctx.table_updates):
+            self.kernels.scatter_i32(group.table, index, page)
+        logits = self.model.forward(ctx, cache)
+        for e, start in zip(entries, starts):
+            cache.commit(e.request_id, start + len(e.tokens))
+        self.steps += 1
+        self.tokens_run += ctx.num_tokens
+        self.last_ctx = ctx
+        return logits

@@ -1,0 +1,87 @@
+"""Grouped-query causal attention over a paged key/value cache.
+
+q, k, v = h Wq^T + bq, h Wk^T + bk, h Wv^T + bv (biases by tensor presence,
+runtime/backends/cuda/native/weight_map.cpp:55-58); q and k are rotated after the
+bias (runtime/backends/cuda/native/transformer_forward.cu:2024-2089); rotated keys
+and raw values go to the cache at the token's position (runtime/backends/cuda/native/
+kernels/fused_rope_kv_append.cuh:110-143); query head h uses key/value head
+h // (heads / kv_heads), score = q.k * scale, every token sees the keys up to its
+own position, or the last `window` of them (runtime/backends/cuda/kernels/
+flash_attention.cu:71-86, 152-172); then the output projection.
+
+The three projections are stacked at load so that one product makes q, k and v.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from ..weights.loader import TensorSpec
+from .base import KVCacheSpec, Mixer, build_part, register_part
+
+
+@register_part("mixer", "attention")
+class Attention(Mixer):
+    """params: hidden_size, num_heads, num_kv_heads, head_dim, window (None or int),
+    position (a PartSpec of role `position`, or None), qkv_bias (True, False or
+    "if_present"), scale (None for 1/sqrt(head_dim))."""
+
+    def __init__(self, spec):
+        super().__init__(spec)
+        p = spec.params
+        self.hidden = int(p["hidden_size"])
+        self.nq = int(p["num_heads"])
+        self.nkv = int(p["num_kv_heads"])
+        self.d = int(p["head_dim"])
+        if self.nq % self.nkv:
+            raise ValueError(f"attention: {self.nq} heads are not a multiple of {self.nkv} kv heads")
+        self.window = None if p.get("window") is None else int(p["window"])
+        self.scale = float(p["scale"]) if p.get("scale") is not None else 1.0 / math.sqrt(self.d)
+        self.qkv_bias = p.get("qkv_bias", "if_present")
+        pos = p.get("position")
+        self.position = build_part("position", pos) if pos is not None else None
+        self.w_qkv = self.b_qkv = self.w_o = None
+
+    # ---------------------------------------------------------------- declarations
+    def cache_spec(self):
+        return KVCacheSpec(self.nkv, self.d, self.window)
+
+    def param_specs(self):
+        q, kv = self.nq * self.d, self.nkv * self.d
+        specs = {
+            "q_proj.weight": TensorSpec((q, self.hidden)),
+            "k_proj.weight": TensorSpec((kv, self.hidden)),
+            "v_proj.weight": TensorSpec((kv, self.hidden)),
+            "o_proj.weight": TensorSpec((self.hidden, q)),
+        }
+        if self.qkv_bias is not False:
+            optional = self.qkv_bias == "if_present"
+            specs["q_proj.bias"] = TensorSpec((q,), optional=optional)
+            specs["k_proj.bias"] = TensorSpec((kv,), optional=optional)
+            specs["v_proj.bias"] = TensorSpec((kv,), optional=optional)
+        return specs
+
+    def load(self, tensors, dtype, device):
+        mats = [tensors[n + "_proj.weight"].to(device=device, dtype=dtype) for n in ("q", "k", "v")]
+        self.w_qkv = torch.cat(mats, dim=0).contiguous()
+        self.w_o = tensors["o_proj.weight"].to(device=device, dtype=dtype).contiguous()
+        sizes = (self.nq * self.d, self.nkv * self.d, self.nkv * self.d)
+        if any((n + "_proj.bias") in tensors for n in ("q", "k", "v")):
+            parts = []
+            for n, size in zip(("q", "k", "v"), sizes):
+                b = tensors.get(n + "_proj.bias")
+                parts.append(torch.zeros(size, dtype=torch.float32, device=device) if b is None
+                             else b.to(device=device, dtype=torch.float32))
+            self.b_qkv = torch.cat(parts).contiguous()      # added in float32
+        else:
+            self.b_qkv = None
+
+    # --------------------------------------------------------------------- forward
+    def forward(self, h, ctx, cache):
+        k = ctx.kernels
+        qkv = k.linear(h, self.w_qkv)                                        # [T, (nq + 2 nkv) d]
+        rotary = self.position.rotary(h.device) if self.position is not None else None
+        q = k.rope_append(qkv, self.b_qkv, rotary, self.nq, self.nkv, self.d, ctx, cache)   # [T, nq d]
+        a = k.attention(q, self.nq, self.nkv, self.d, self.window, self.scale, ctx, cache)  # [T, nq d]
+        return k.linear(a, self.w_o)

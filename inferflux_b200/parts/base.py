@@ -1,0 +1,138 @@
+"""Interfaces of the parts a layer is made of, and the registries that map a part's
+kind name to its class.
+
+A part is built from a `PartSpec` (kind + parameters): it never learns which model
+it is in.  It declares the tensors it needs (`param_specs`), takes them (`load`) and
+does its work through the kernel table of the step (`ctx.kernels`).
+
+    Norm              forward(x, delta=None, ctx) -> h
+    PositionEncoding  rotary() -> RotaryTable or None
+    Mixer             cache_spec() / state_spec(); forward(h, ctx, cache) -> y
+    FeedForward       forward(h, ctx) -> y
+    Block             forward(x, pending, ctx, cache) -> (x, pending)
+
+`x` is the float32 residual stream [tokens, hidden]; `h` and `y` are in the dtype
+the run computes in.  `pending` is a delta that has not been added to `x` yet, so
+that the next norm can add it and normalise in one kernel.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Callable, Dict, Optional, Tuple
+
+import torch
+
+from ..config.plan import PartSpec
+from ..weights.loader import TensorSpec
+
+
+# --------------------------------------------------------------------- cache needs
+
+@dataclass(frozen=True)
+class KVCacheSpec:
+    """What a mixer stores per token: keys and values of `num_kv_heads` heads of
+    `head_dim`; `window` None keeps every key, an integer only the last `window`."""
+    num_kv_heads: int
+    head_dim: int
+    window: Optional[int] = None
+
+
+@dataclass(frozen=True)
+class StateSpec:
+    """What a mixer stores per request, whatever the request's length."""
+    shape: Tuple[int, ...]
+    dtype: torch.dtype = torch.float32
+
+
+@dataclass
+class RotaryTable:
+    """A rotation of the first `rotary_dim` elements of every head: inverse
+    frequencies [rotary_dim / 2] in float32 and how elements pair up."""
+    inv_freq: torch.Tensor
+    rotary_dim: int
+    interleaved: bool            # False: (i, i + rotary_dim/2); True: (2i, 2i+1)
+
+
+# --------------------------------------------------------------------------- parts
+
+class Part:
+    """Base of all parts."""
+
+    def __init__(self, spec: PartSpec):
+        self.spec = spec
+
+    def param_specs(self) -> Dict[str, TensorSpec]:
+        """Tensor names (relative to the part's prefix) this part expects."""
+        return {}
+
+    def load(self, tensors: Dict[str, torch.Tensor], dtype: torch.dtype, device) -> None:
+        """Take the tensors named by `param_specs` (absent optional ones are left
+        out of `tensors`) and keep them in the form the kernels want."""
+
+
+class Norm(Part):
+    def forward(self, x: torch.Tensor, delta: Optional[torch.Tensor], ctx) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class PositionEncoding(Part):
+    def rotary(self, device) -> Optional[RotaryTable]:
+        """The rotation the mixer applies to queries and keys, or None."""
+        return None
+
+
+class Mixer(Part):
+    def cache_spec(self) -> Optional[KVCacheSpec]:
+        return None
+
+    def state_spec(self) -> Optional[StateSpec]:
+        return None
+
+    def forward(self, h: torch.Tensor, ctx, cache) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    def forward(self, h: torch.Tensor, ctx) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class Block(Part):
+    """Arrangement of two norms, a mixer and a feed-forward around the residual."""
+
+    def __init__(self, spec, mixer: Mixer, ffn: FeedForward, norm_mixer: Norm, norm_ffn: Norm):
+        super().__init__(spec)
+        self.mixer, self.ffn, self.norm_mixer, self.norm_ffn = mixer, ffn, norm_mixer, norm_ffn
+
+    def forward(self, x, pending, ctx, cache):
+        raise NotImplementedError
+
+
+# ---------------------------------------------------------------------- registries
+
+_REGISTRIES: Dict[str, Dict[str, type]] = {
+    "mixer": {}, "ffn": {}, "norm": {}, "position": {}, "block": {}, "embedding": {}, "lm_head": {},
+}
+
+
+def register_part(role: str, kind: str) -> Callable[[type], type]:
+    """Class decorator: make `kind` available for `role` (mixer, ffn, norm,
+    position, block, embedding, lm_head)."""
+    if role not in _REGISTRIES:
+        raise KeyError(f"unknown part role {role!r}; roles: {sorted(_REGISTRIES)}")
+
+    def deco(cls: type) -> type:
+        _REGISTRIES[role][kind] = cls
+        return cls
+    return deco
+
+
+def build_part(role: str, spec: PartSpec, *args, **kwargs):
+    table = _REGISTRIES[role]
+    if spec.kind not in table:
+        raise KeyError(f"no {role} of kind {spec.kind!r} is registered; known: {sorted(table)}")
+    return table[spec.kind](spec, *args, **kwargs)
+
+
+def registered_parts(role: str):
+    return sorted(_REGISTRIES[role])

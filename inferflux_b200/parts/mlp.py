@@ -1,0 +1,39 @@
+"""SwiGLU feed-forward: (silu(h Wg^T) * (h Wu^T)) Wd^T, no biases
+(runtime/backends/cuda/native/transformer_forward.cu:2384-2535).  Gate and up
+weights are stacked at load so that one product makes both."""
+from __future__ import annotations
+
+import torch
+
+from ..weights.loader import TensorSpec
+from .base import FeedForward, register_part
+
+
+@register_part("ffn", "swiglu")
+class SwiGLU(FeedForward):
+    """params: hidden_size, intermediate_size."""
+
+    def __init__(self, spec):
+        super().__init__(spec)
+        self.hidden = int(spec.params["hidden_size"])
+        self.inter = int(spec.params["intermediate_size"])
+        self.w_gate_up = None
+        self.w_down = None
+
+    def param_specs(self):
+        return {
+            "gate_proj.weight": TensorSpec((self.inter, self.hidden)),
+            "up_proj.weight": TensorSpec((self.inter, self.hidden)),
+            "down_proj.weight": TensorSpec((self.hidden, self.inter)),
+        }
+
+    def load(self, tensors, dtype, device):
+        self.w_gate_up = torch.cat([tensors["gate_proj.weight"].to(device=device, dtype=dtype),
+                                    tensors["up_proj.weight"].to(device=device, dtype=dtype)], dim=0).contiguous()
+        self.w_down = tensors["down_proj.weight"].to(device=device, dtype=dtype).contiguous()
+
+    def forward(self, h, ctx):
+        k = ctx.kernels
+        gate_up = k.linear(h, self.w_gate_up)            # [T, 2I]: gate | up
+        act = k.silu_mul(gate_up)                        # [T, I]
+        return k.linear(act, self.w_down)

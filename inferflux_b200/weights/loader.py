@@ -1,0 +1,88 @@
+"""Weights by tensor name, checked against what the model's parts expect.
+
+The reference resolves exact HF names and reports only the first missing layer,
+without checking shapes (runtime/backends/cuda/native/weight_map.cpp:21-75).  Here
+every expected tensor is declared by the part that owns it (name, shape, whether it
+may be absent), and one `WeightError` lists everything that is missing, unexpected
+or wrongly shaped.
+
+Stored dtypes: 16-bit floats are kept as bfloat16, a tensor stored in 32-bit floats
+stays 32-bit, integer tables become int32.  Converting to the dtype a run computes
+in is the part's business when it takes its tensors.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Dict, Optional, Tuple
+
+import torch
+
+from .safetensors_io import open_model_shards
+
+
+@dataclass(frozen=True)
+class TensorSpec:
+    """What a part expects of one tensor."""
+    shape: Tuple[int, ...]
+    init: str = "normal"        # how random-weights mode fills it: normal | ones | zeros
+    optional: bool = False      # may be absent from the file (the part then does without it)
+    ignored: bool = False       # may be present but is not used (e.g. lm_head.weight of a tied model)
+
+
+class WeightError(ValueError):
+    """Missing, unexpected or wrongly shaped tensors, all in one message."""
+
+    def __init__(self, missing, unexpected, wrong_shape, where=""):
+        self.missing = sorted(missing)
+        self.unexpected = sorted(unexpected)
+        self.wrong_shape = sorted(wrong_shape)
+        lines = [f"weights of {where} do not match the configuration:" if where
+                 else "weights do not match the configuration:"]
+        if self.missing:
+            lines.append(f"  missing ({len(self.missing)}): " + ", ".join(self.missing))
+        if self.unexpected:
+            lines.append(f"  unexpected ({len(self.unexpected)}): " + ", ".join(self.unexpected))
+        if self.wrong_shape:
+            lines.append(f"  wrong shape ({len(self.wrong_shape)}): " + ", ".join(
+                f"{n} is {list(got)}, expected {list(want)}" for n, got, want in self.wrong_shape))
+        super().__init__("\n".join(lines))
+
+
+def stored_dtype(dt: torch.dtype) -> torch.dtype:
+    """The dtype a tensor of file dtype `dt` is kept in."""
+    if dt in (torch.float32, torch.float64):
+        return torch.float32
+    if dt.is_floating_point:
+        return torch.bfloat16
+    return torch.int32
+
+
+def check_tensors(found: Dict[str, Tuple[int, ...]], expected: Dict[str, TensorSpec], where: str = "") -> None:
+    """Raise one WeightError if the shapes in `found` do not fit `expected`."""
+    missing = [n for n, s in expected.items() if n not in found and not s.optional and not s.ignored]
+    unexpected = [n for n in found if n not in expected]
+    wrong = [(n, tuple(found[n]), tuple(s.shape)) for n, s in expected.items()
+             if n in found and not s.ignored and tuple(found[n]) != tuple(s.shape)]
+    if missing or unexpected or wrong:
+        raise WeightError(missing, unexpected, wrong, where)
+
+
+def load_weights(model_dir, expected: Dict[str, TensorSpec], device="cpu") -> Dict[str, torch.Tensor]:
+    """All tensors of a model folder that `expected` names, on `device`."""
+    shards = open_model_shards(model_dir)
+    try:
+        owner = {}
+        for sh in shards:
+            for n in sh.names():
+                owner.setdefault(n, sh)          # first occurrence of a name wins, as in the reference
+        check_tensors({n: sh.shape(n) for n, sh in owner.items()}, expected, where=str(model_dir))
+        out = {}
+        for n, spec in expected.items():
+            if n not in owner or spec.ignored:
+                continue
+            t = owner[n].tensor(n)
+            out[n] = t.to(stored_dtype(t.dtype)).to(device)
+        return out
+    finally:
+        for sh in shards:
+            sh.close()
