@@ -1,5 +1,8 @@
 """Step function, scheduler and the Python entry point."""
 from .batch import StepContext, StepEntry
+from .engine import Engine, EngineStats, GenerationResult
 from .runner import ModelRunner, StepError
+from .scheduler import Request, Scheduler, SchedulerConfig, StepPlan
 
-__all__ = ["StepContext", "StepEntry", "ModelRunner", "StepError"]
+__all__ = ["StepContext", "StepEntry", "Engine", "EngineStats", "GenerationResult", "ModelRunner", "StepError",
+           "Request", "Scheduler", "SchedulerConfig", "StepPlan"]

@@ -1,0 +1,183 @@
+"""The Python entry point: from a model folder (or a configuration and a seed) to
+generated token ids on one GPU.
+
+The reference has no Python binding; its in-process surface is
+NativeGpuBackend::LoadModel / Generate (runtime/backends/native/
+native_gpu_backend.cpp:76-167, 594-834) and Scheduler::Generate
+(scheduler/scheduler.cpp:1763).  Option names follow the reference where it has
+them: SamplingParams fields (scheduler/request_batch.h:26-38), the scheduler's
+max_batch_size / max_batch_tokens / chunked_prefill_tokens /
+mixed_prefill_budget_ratio (scheduler/scheduler.h:74-84), `max_tokens` (default 256,
+cli/main.cpp:1587), and the cache sizing knobs kv_max_batch / kv_max_seq /
+kv_budget_mb / kv_budget_ratio (runtime/backends/cuda/native/
+native_bootstrap_config.h:10-20) with 16-token pages (scheduler/scheduler.cpp:293).
+"""
+from __future__ import annotations
+
+import random
+from dataclasses import dataclass, field
+from typing import Hashable, List, Optional, Sequence, Union
+
+import torch
+
+from ..models.loading import load_model, parse_dtype, random_model
+from ..sampling import Sampler, SamplingParams, SamplingRow
+from .runner import ModelRunner
+from .scheduler import Request, Scheduler, SchedulerConfig
+
+
+@dataclass
+class GenerationResult:
+    request_id: Hashable
+    prompt_tokens: int
+    token_ids: List[int]
+    finish_reason: str
+    preemptions: int = 0
+
+    @property
+    def completion_tokens(self) -> int:
+        return len(self.token_ids)
+
+
+@dataclass
+class EngineStats:
+    steps: int = 0
+    prompt_tokens: int = 0
+    generated_tokens: int = 0
+    preemptions: int = 0
+    h2d_bytes: int = 0
+    d2h_bytes: int = 0
+
+
+class Engine:
+    def __init__(self, model=None, dtype="bfloat16", device="cuda:0", *, config=None, seed: int = 0,
+                 kernels=None, kv_page_size: int = 16, kv_num_pages: Optional[int] = None,
+                 kv_max_batch: int = 16, kv_max_seq: Optional[int] = None, kv_budget_mb: Optional[float] = None,
+                 kv_budget_ratio: float = 0.20, max_batch_size: int = 32, max_batch_tokens: int = 16384,
+                 chunked_prefill_tokens: int = 512, mixed_prefill_budget_ratio: float = 1.0,
+                 sampling_seed: int = 0, loaded_model=None):
+        """`model`: a folder with config.json and model.safetensors.  Without it,
+        `config` (a typed configuration) and `seed` make random weights on the device."""
+        self.device = torch.device(device)
+        self.dtype = parse_dtype(dtype)
+        if kernels is None:
+            from ..csrc import CudaKernels            # raises if the library cannot be built or no GPU is there
+            kernels = CudaKernels(self.device)
+        self.kernels = kernels
+        if self.device.type == "cuda":
+            torch.cuda.set_device(self.device)
+        if loaded_model is not None:
+            self.config, self.model = config, loaded_model
+        elif model is not None:
+            self.config, self.model = load_model(model, dtype=self.dtype, device=self.device)
+        elif config is not None:
+            self.config, self.model = config, random_model(config, seed=seed, dtype=self.dtype, device=self.device)
+        else:
+            raise ValueError("Engine needs a model folder, or a configuration for random weights")
+
+        max_seq = min(self.model.plan.max_positions, kv_max_seq) if kv_max_seq else self.model.plan.max_positions
+        max_seqs = max(int(kv_max_batch), 1)
+        if kv_num_pages is None:
+            kv_num_pages = self._plan_pages(kv_page_size, max_seqs, max_seq, kv_budget_mb, kv_budget_ratio)
+        self.runner = ModelRunner(self.model, kernels, page_size=kv_page_size, num_pages=kv_num_pages,
+                                  max_seqs=max_seqs, max_seq_len=max_seq)
+        self.scheduler = Scheduler(SchedulerConfig(max_batch_size=min(max_batch_size, max_seqs),
+                                                   max_batch_tokens=max_batch_tokens,
+                                                   chunked_prefill_tokens=chunked_prefill_tokens,
+                                                   mixed_prefill_budget_ratio=mixed_prefill_budget_ratio),
+                                   self.runner.cache, max_seq)
+        self.sampler = Sampler(kernels, self.device)
+        self._rng = random.Random(sampling_seed)
+        self._next_id = 0
+        self.stats = EngineStats()
+
+    # ------------------------------------------------------------------ sizing
+    def bytes_per_token(self) -> int:
+        """Cache bytes one token takes over all caches (2 . layers . kv_heads . head_dim . itemsize
+        for a plain decoder, runtime/backends/cuda/native/kv_cache_planner.h:22-37)."""
+        item = torch.empty(0, dtype=self.dtype).element_size()
+        return sum(2 * kv.num_kv_heads * kv.head_dim * item for kv, _st in self.model.cache_specs() if kv)
+
+    def _plan_pages(self, page_size, max_seqs, max_seq, budget_mb, ratio) -> int:
+        per_page = max(1, self.bytes_per_token() * page_size)
+        if budget_mb is not None:
+            budget = int(budget_mb * 1024 * 1024)
+        elif self.device.type == "cuda":
+            free, _total = torch.cuda.mem_get_info(self.device)
+            budget = int(free * ratio)
+        else:
+            budget = 64 * 1024 * 1024
+        pages = budget // per_page
+        most = max_seqs * (-(-max_seq // page_size))          # more than this can never be in use
+        return int(max(1, min(pages, most)))
+
+    # ---------------------------------------------------------------- requests
+    def add_request(self, prompt_token_ids: Sequence[int], sampling_params: Optional[SamplingParams] = None,
+                    max_tokens: int = 256, eos_token_id: Union[None, int, Sequence[int]] = None,
+                    request_id: Optional[Hashable] = None) -> Hashable:
+        params = sampling_params or SamplingParams()
+        vocab = self.model.plan.vocab_size
+        prompt = [int(t) for t in prompt_token_ids]
+        bad = [t for t in prompt if not 0 <= t < vocab]
+        if bad:
+            raise ValueError(f"prompt token ids {bad[:8]} are outside the vocabulary of {vocab}")
+        if request_id is None:
+            request_id = f"req-{self._next_id}"
+        self._next_id += 1
+        eos = () if eos_token_id is None else ((eos_token_id,) if isinstance(eos_token_id, int) else tuple(eos_token_id))
+        seed = params.seed if params.seed is not None else self._rng.getrandbits(63)
+        self.scheduler.add(Request(request_id, prompt, params, max_tokens=max_tokens, eos_token_ids=eos, seed=seed))
+        return request_id
+
+    def has_unfinished(self) -> bool:
+        return self.scheduler.has_unfinished()
+
+    # -------------------------------------------------------------------- step
+    def step(self) -> List[GenerationResult]:
+        """One scheduler decision, one model step, one sampling call.  Returns the
+        requests that finished in it (failed ones included)."""
+        plan = self.scheduler.schedule()
+        results = [self._result(r) for r in plan.failed]
+        if not plan.entries:
+            return results
+        entries = plan.step_entries()
+        logits = self.runner.step(entries)
+        rows = [SamplingRow(e.request.params, e.request.seed, len(e.request.output), e.request.output)
+                for e in plan.entries if e.wants_logits]
+        sampled: List[int] = []
+        if rows:
+            ids = self.sampler.sample(logits, rows)
+            sampled = ids.tolist()                          # the step's device-to-host read
+            self.stats.d2h_bytes += 4 * len(sampled)
+        self.stats.h2d_bytes += self.runner.last_ctx.meta_bytes
+        self.stats.steps += 1
+        self.stats.prompt_tokens += sum(e.count for e in plan.entries if e.count > 1 or not e.request.output)
+        self.stats.generated_tokens += len(sampled)
+        self.stats.preemptions = self.scheduler.num_preemptions
+        for r in self.scheduler.update(plan, sampled):
+            results.append(self._result(r))
+        return results
+
+    @staticmethod
+    def _result(r: Request) -> GenerationResult:
+        return GenerationResult(r.request_id, len(r.prompt), list(r.output), r.finish_reason or "", r.preemptions)
+
+    # ---------------------------------------------------------------- generate
+    def generate(self, prompts: Sequence[Sequence[int]],
+                 sampling_params: Union[None, SamplingParams, Sequence[SamplingParams]] = None,
+                 max_tokens: int = 256, eos_token_id=None) -> List[GenerationResult]:
+        """Generate for every prompt (lists of token ids); results come back in the
+        order of the prompts."""
+        if sampling_params is None or isinstance(sampling_params, SamplingParams):
+            sampling_params = [sampling_params] * len(prompts)
+        ids = [self.add_request(p, sp, max_tokens=max_tokens, eos_token_id=eos_token_id)
+               for p, sp in zip(prompts, sampling_params)]
+        done = {}
+        guard = 0
+        while self.has_unfinished():
+            for res in self.step():
+                done[res.request_id] = res
+            guard += 1
+            if guard > 10_000_000:
+                raise RuntimeError("generation did not finish")
+        return [done[i] for i in ids]

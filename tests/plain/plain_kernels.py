@@ -177,6 +177,7 @@ def philox_uniform(key0, key1, c0, c1=0, c2=0, c3=0):
     """First word of Philox4x32-10 as a float in [0, 1) with 24 bits."""
     M0, M1, W0, W1 = 0xD2511F53, 0xCD9E8D57, 0x9E3779B9, 0xBB67AE85
     mask = 0xFFFFFFFF
+    key0, key1, c0, c1, c2, c3 = (v & mask for v in (key0, key1, c0, c1, c2, c3))
     for _ in range(10):
         p0, p1 = M0 * c0, M1 * c2
         hi0, lo0, hi1, lo1 = p0 >> 32, p0 & mask, p1 >> 32, p1 & mask

@@ -1,0 +1,293 @@
+"""Each CUDA kernel alone against its plain statement, at sizes other than the
+engine's tiny models: widths and vocabularies that are no power of two, head sizes
+in steps of 16, odd head counts and groups, sharp attention data, page edges."""
+import math
+
+import pytest
+import torch
+
+from plain.plain_kernels import PlainKernels, philox_uniform
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def rnd(*shape, dtype=torch.float32, seed=0, scale=1.0):
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    return (torch.randn(*shape, generator=g) * scale).to(dtype).to(DEV)
+
+
+def close(a, b, atol, rtol=0.0):
+    a, b = a.double(), b.double()
+    assert torch.isfinite(a).all() and torch.isfinite(b).all(), "non-finite values: the inputs are broken"
+    err = (a - b).abs()
+    bound = atol + rtol * b.abs()
+    assert bool((err <= bound).all()), f"max err {float(err.max())}, at {int(err.argmax())}, bound {atol}+{rtol}*|b|"
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("hidden,vocab", [(72, 301), (1000, 50), (3584, 777)])
+def test_embed(cuda_kernels, dtype, hidden, vocab):
+    table = rnd(vocab, hidden, dtype=dtype)
+    ids = torch.randint(0, vocab, (37,), dtype=torch.int32, device=DEV)
+    assert torch.equal(cuda_kernels.embed(table, ids, vocab), PlainKernels().embed(table, ids, vocab))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("rows,hidden,eps", [(1, 64, 1e-6), (19, 200, 1e-5), (5, 3584, 1e-6), (3, 5000, 3e-4)])
+def test_rmsnorm_and_fused_add(cuda_kernels, dtype, rows, hidden, eps):
+    x = rnd(rows, hidden, seed=1, scale=0.05)
+    w = 1.0 + rnd(hidden, seed=2, scale=0.3)
+    want = PlainKernels(wide=True).rmsnorm(x, w, eps, torch.float64)
+    got = cuda_kernels.rmsnorm(x, w, eps, dtype)
+    close(got, want, atol=2e-6, rtol=2e-6 if dtype == torch.float32 else 2 ** -8)
+    delta = rnd(rows, hidden, dtype=dtype, seed=3, scale=0.05)
+    x1, x2 = x.clone(), x.clone()
+    want = PlainKernels(wide=True).add_rmsnorm(x1, delta, w, eps, torch.float64)
+    got = cuda_kernels.add_rmsnorm(x2, delta, w, eps, dtype)
+    assert torch.equal(x1, x2), "the residual stream after the add differs"
+    close(got, want, atol=2e-6, rtol=2e-6 if dtype == torch.float32 else 2 ** -8)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("rows,inter", [(3, 176), (17, 321), (2, 18944)])
+def test_silu_mul(cuda_kernels, dtype, rows, inter):
+    gu = rnd(rows, 2 * inter, dtype=dtype, seed=4, scale=2.0)
+    want = PlainKernels(wide=True).silu_mul(gu.double())
+    close(cuda_kernels.silu_mul(gu), want, atol=1e-6, rtol=1e-6 if dtype == torch.float32 else 2 ** -8)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_residual_add_gather_scatter(cuda_kernels, dtype):
+    x = rnd(13, 100, seed=5)
+    delta = rnd(13, 100, dtype=dtype, seed=6)
+    want = x + delta.float()
+    cuda_kernels.residual_add(x, delta)
+    assert torch.equal(x, want)
+    rows = torch.tensor([12, 0, 5, 5], dtype=torch.int32, device=DEV)
+    assert torch.equal(cuda_kernels.gather_rows(x, rows), x[rows.long()])
+    table = torch.zeros((4, 10), dtype=torch.int32, device=DEV)
+    idx = torch.tensor([3, 17, 39], dtype=torch.int32, device=DEV)
+    val = torch.tensor([7, 8, 9], dtype=torch.int32, device=DEV)
+    cuda_kernels.scatter_i32(table, idx, val)
+    assert table.view(-1)[idx.long()].tolist() == [7, 8, 9] and int(table.sum()) == 24
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 64, 64), (7, 130, 50), (65, 257, 333), (130, 1000, 192), (3, 48, 17)])
+def test_gemm_float32(cuda_kernels, M, N, K):
+    a, w, b = rnd(M, K, seed=7), rnd(N, K, seed=8), rnd(N, seed=9)
+    want = a.double() @ w.double().t() + b.double()
+    close(cuda_kernels.linear(a, w, b), want, atol=1e-5 * math.sqrt(K), rtol=1e-6)
+    # a row's result does not depend on what else is in the launch
+    alone = cuda_kernels.linear(a[M // 2:M // 2 + 1].contiguous(), w, b)
+    assert torch.equal(alone[0], cuda_kernels.linear(a, w, b)[M // 2])
+
+
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("M,N,K", [(1, 64, 64), (7, 136, 48), (65, 264, 328), (8, 1000, 192), (3, 50, 17)])
+def test_gemm_bfloat16(cuda_kernels, M, N, K, out_dtype):
+    a, w = rnd(M, K, dtype=torch.bfloat16, seed=7), rnd(N, K, dtype=torch.bfloat16, seed=8)
+    want = a.double() @ w.double().t()
+    rtol = 2 ** -8 if out_dtype == torch.bfloat16 else 1e-5
+    close(cuda_kernels.linear(a, w, out_dtype=out_dtype), want, atol=1e-4 * math.sqrt(K), rtol=rtol)
+    close(cuda_kernels.linear_generic(a, w, out_dtype=out_dtype), want, atol=1e-4 * math.sqrt(K), rtol=rtol)
+
+
+# ---------------------------------------------------------------------- attention
+
+class _Ctx:
+    pass
+
+
+def make_cache_case(dtype, nkv, d, page, lens, spans, num_pages, seed, shuffle=True):
+    """A cache filled by hand: `lens[r]` tokens stored for request r, of which the
+    last `spans[r]` are this step's queries.  Pages are handed out in a shuffled
+    order so that logical and physical order differ."""
+    from inferflux_b200.cache.manager import CacheView
+    g = torch.Generator().manual_seed(seed)
+    R = len(lens)
+    max_blocks = max(-(-n // page) for n in lens) + 1
+    order = torch.randperm(num_pages, generator=g).tolist() if shuffle else list(range(num_pages))
+    table = torch.full((R + 2, max_blocks), -1, dtype=torch.int32)
+    slots = list(range(R, 0, -1))                       # slots differ from batch order
+    for r, n in enumerate(lens):
+        for b in range(-(-n // page)):
+            table[slots[r], b] = order.pop()
+    kv = torch.zeros((num_pages, 2, nkv, page, d), dtype=dtype)
+    ctx = _Ctx()
+    positions, token_req = [], []
+    for r, (n, s) in enumerate(zip(lens, spans)):
+        positions += list(range(n - s, n))
+        token_req += [r] * s
+    ctx.positions = torch.tensor(positions, dtype=torch.int32, device=DEV)
+    ctx.token_req = torch.tensor(token_req, dtype=torch.int32, device=DEV)
+    ctx.req_slot = torch.tensor(slots, dtype=torch.int32, device=DEV)
+    ctx.num_tokens = len(positions)
+    cache = CacheView(kv.to(DEV), table.to(DEV), page, None, True, 0)
+    return ctx, cache, slots
+
+
+def fill_cache(cache, lens, slots, nkv, d, dtype, seed, sharp_every=0):
+    """Random keys and values for every stored position; returns them per request."""
+    g = torch.Generator().manual_seed(seed)
+    page = cache.page_size
+    stored = []
+    for r, n in enumerate(lens):
+        K = torch.randn(n, nkv, d, generator=g).to(dtype)
+        V = torch.randn(n, nkv, d, generator=g).to(dtype)
+        stored.append((K, V))
+        for p in range(n):
+            pg = int(cache.block_table[slots[r], p // page])
+            cache.kv[pg, 0, :, p % page, :] = K[p].to(DEV)
+            cache.kv[pg, 1, :, p % page, :] = V[p].to(DEV)
+    return stored
+
+
+def attention_oracle(q, stored, lens, spans, nq, nkv, d, window, scale):
+    out = []
+    t = 0
+    for r, (n, s) in enumerate(zip(lens, spans)):
+        K, V = stored[r][0].double(), stored[r][1].double()
+        for pos in range(n - s, n):
+            first = max(0, pos - window + 1) if window else 0
+            for h in range(nq):
+                g = h // (nq // nkv)
+                sc = (K[first:pos + 1, g] @ q[t, h].double().cpu()) * scale
+                out.append(torch.softmax(sc, 0) @ V[first:pos + 1, g])
+            t += 1
+    return torch.stack(out).view(-1, nq * d)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("nq,nkv,d,page,window", [
+    (4, 2, 16, 4, None), (6, 2, 32, 8, None), (7, 1, 128, 16, None), (5, 5, 48, 16, 21),
+    (28, 4, 128, 16, None), (12, 2, 64, 32, 100), (3, 1, 80, 8, 7), (2, 1, 256, 16, None)])
+def test_attention_over_pages(cuda_kernels, dtype, nq, nkv, d, page, window):
+    """Mixed spans (prompt portions beside single tokens) over shuffled pages, with
+    sharp data: one far key per query dominates, so a key that is missed, read from
+    the wrong page or masked wrongly changes the result."""
+    lens = [1, 37, 130, 64, 259, 16]
+    spans = [1, 1, 50, 64, 3, 2]
+    ctx, cache, slots = make_cache_case(dtype, nkv, d, page, lens, spans, num_pages=80 if page >= 8 else 200,
+                                        seed=3)
+    stored = fill_cache(cache, lens, slots, nkv, d, dtype, seed=4)
+    T = ctx.num_tokens
+    q = rnd(T, nq, d, dtype=dtype, seed=5, scale=0.3)
+    # plant: query t of head h looks hard at one key inside its range (often the first or last it may see)
+    t = 0
+    for r, (n, s) in enumerate(zip(lens, spans)):
+        for pos in range(n - s, n):
+            first = max(0, pos - window + 1) if window else 0
+            target = [first, pos, (first + pos) // 2][t % 3]
+            for h in range(nq):
+                g = h // (nq // nkv)
+                q[t, h] = (stored[r][0][target, g].float() * (12.0 / math.sqrt(d))).to(dtype).to(DEV)
+            t += 1
+    scale = 1.0 / math.sqrt(d)
+    want = attention_oracle(q, stored, lens, spans, nq, nkv, d, window, scale)
+    got = cuda_kernels.attention(q.view(T, nq * d), nq, nkv, d, window, scale, ctx, cache)
+    close(got.cpu(), want, atol=2e-5 if dtype == torch.float32 else 2e-2, rtol=1e-5 if dtype == torch.float32 else 2e-2)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("nq,nkv,d,rot,interleaved,bias", [
+    (4, 2, 16, 16, False, True), (6, 2, 32, 32, False, False), (5, 1, 48, 24, True, True),
+    (28, 4, 128, 128, False, True), (3, 3, 80, 0, False, True)])
+def test_rope_append(cuda_kernels, dtype, nq, nkv, d, rot, interleaved, bias):
+    from inferflux_b200.parts.base import RotaryTable
+    page = 8
+    lens, spans = [5, 300, 41, 17], [5, 1, 30, 2]
+    ctx, cache, slots = make_cache_case(dtype, nkv, d, page, lens, spans, num_pages=60, seed=6)
+    ref_cache_kv = cache.kv.clone()
+    T = ctx.num_tokens
+    qkv = rnd(T, (nq + 2 * nkv) * d, dtype=dtype, seed=7)
+    b = rnd((nq + 2 * nkv) * d, seed=8, scale=0.5) if bias else None
+    rotary = None
+    if rot:
+        inv = (1.0 / (1e6 ** (torch.arange(0, rot, 2, dtype=torch.float32) / rot))).to(DEV)
+        rotary = RotaryTable(inv, rot, interleaved)
+    q_got = cuda_kernels.rope_append(qkv, b, rotary, nq, nkv, d, ctx, cache)
+    got_kv = cache.kv.clone()
+    cache.kv = ref_cache_kv
+    q_want = PlainKernels(wide=True).rope_append(qkv, b, rotary, nq, nkv, d, ctx, cache)
+    tol = dict(atol=3e-5, rtol=1e-5) if dtype == torch.float32 else dict(atol=1e-2, rtol=2 ** -7)
+    close(q_got, q_want, **tol)
+    close(got_kv, cache.kv, **tol)
+    assert int((got_kv != 0).any(-1).sum()) == int((cache.kv != 0).any(-1).sum()), "rows written differ"
+
+
+# ----------------------------------------------------------------------- sampling
+
+@pytest.mark.parametrize("rows,vocab", [(1, 512), (5, 1000), (64, 152064), (3, 777)])
+def test_argmax_first_index_wins(cuda_kernels, rows, vocab):
+    logits = rnd(rows, vocab, seed=10)
+    logits[0, vocab // 3] = 50.0
+    logits[0, vocab - 1] = 50.0                      # a tie: the lower index is the answer
+    got = cuda_kernels.argmax(logits)
+    assert got.tolist() == torch.argmax(logits, -1).tolist()
+    assert int(got[0]) == vocab // 3
+
+
+def test_sampling_matches_plain(cuda_kernels):
+    from plain.plain_kernels import PlainKernels
+    rows, vocab = 12, 3001
+    logits = rnd(rows, vocab, seed=11, scale=3.0)
+    f = lambda v: torch.tensor(v, dtype=torch.float32, device=DEV)
+    i = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    temperature = f([0.8, 1.0, 0.0, 1.3, 0.5, 1.0, 1.0, 0.7, 1.0, 2.0, 1.0, 0.9])
+    top_k = i([0, 40, 0, 0, 5, 0, 1, 0, 100, 0, 0, 3])
+    top_p = f([1.0, 1.0, 1.0, 0.9, 1.0, 0.5, 1.0, 0.95, 0.8, 1.0, 0.1, 1.0])
+    min_p = f([0, 0, 0, 0, 0, 0, 0, 0.05, 0, 0.2, 0, 0])
+    seed_lo = torch.arange(rows, dtype=torch.int64).add(12345).to(torch.int32).to(DEV)
+    seed_hi = torch.zeros(rows, dtype=torch.int32, device=DEV)
+    agree = 0
+    for step in range(6):
+        st = torch.full((rows,), step, dtype=torch.int32, device=DEV)
+        got = cuda_kernels.sample(logits, temperature, top_k, top_p, min_p, seed_lo, seed_hi, st).tolist()
+        want = PlainKernels().sample(logits.cpu(), temperature.cpu(), top_k.cpu(), top_p.cpu(), min_p.cpu(),
+                                     seed_lo.cpu(), seed_hi.cpu(), st.cpu()).tolist()
+        agree += sum(int(a == b) for a, b in zip(got, want))
+        assert got[2] == int(torch.argmax(logits[2])) and got[6] == int(torch.argmax(logits[6]))
+        # whatever is drawn must lie inside the kept set
+        from plain.plain_kernels import kept_mask
+        for r in range(rows):
+            if float(temperature[r]) > 0:
+                p = torch.softmax(logits[r].cpu() / float(temperature[r]), -1)
+                keep = kept_mask(p, int(top_k[r]), float(top_p[r]), float(min_p[r]))
+                assert bool(keep[got[r]]) or float(p[got[r]]) >= 0.999 * float(p[keep].min())
+    assert agree >= 6 * rows - 2, f"only {agree} of {6 * rows} draws agree with the plain sampler"
+
+
+def test_sampling_distribution_and_batch_independence(cuda_kernels):
+    vocab = 50
+    logits = torch.log(torch.arange(1, vocab + 1, dtype=torch.float32)).repeat(4096, 1).to(DEV)
+    n = logits.shape[0]
+    f = lambda v: torch.full((n,), v, dtype=torch.float32, device=DEV)
+    z = torch.zeros(n, dtype=torch.int32, device=DEV)
+    seeds = torch.arange(n, dtype=torch.int32, device=DEV)
+    got = cuda_kernels.sample(logits, f(1.0), z, f(1.0), f(0.0), seeds, z, z)
+    freq = torch.bincount(got.long(), minlength=vocab).float() / n
+    want = torch.arange(1, vocab + 1, dtype=torch.float32) / (vocab * (vocab + 1) / 2)
+    assert float((freq.cpu() - want).abs().max()) < 0.015
+    # the same request (seed, step) draws the same token alone as in a batch
+    alone = cuda_kernels.sample(logits[7:8].contiguous(), f(1.0)[:1], z[:1], f(1.0)[:1], f(0.0)[:1],
+                                seeds[7:8].contiguous(), z[:1], z[:1])
+    assert int(alone[0]) == int(got[7])
+    assert abs(philox_uniform(7, 0, 0) - 0.5) <= 0.5
+
+
+def test_penalties_and_bias(cuda_kernels):
+    logits = rnd(2, 100, seed=12)
+    want = logits.clone().cpu()
+    tokens = torch.tensor([[5, 9, -1], [7, -1, -1]], dtype=torch.int32)
+    counts = torch.tensor([[2, 1, 0], [3, 0, 0]], dtype=torch.int32)
+    rep, freq, pres = torch.tensor([1.3, 1.0]), torch.tensor([0.1, 0.5]), torch.tensor([0.2, 0.0])
+    PlainKernels().penalties(want, tokens, counts, rep, freq, pres)
+    cuda_kernels.penalties(logits, tokens.to(DEV), counts.to(DEV), rep.to(DEV), freq.to(DEV), pres.to(DEV))
+    close(logits.cpu(), want, atol=1e-6)
+    rows = torch.tensor([0, 1, 1], dtype=torch.int32, device=DEV)
+    toks = torch.tensor([3, 3, 99], dtype=torch.int32, device=DEV)
+    bias = torch.tensor([1.5, -2.0, 100.0], device=DEV)
+    cuda_kernels.logit_bias(logits, rows, toks, bias)
+    want[0, 3] += 1.5; want[1, 3] -= 2.0; want[1, 99] += 100.0
+    close(logits.cpu(), want, atol=1e-6)

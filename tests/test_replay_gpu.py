@@ -1,0 +1,122 @@
+"""Replay of the same requests cut in every way, in 32-bit and in bfloat16, through
+the step function and through bin/trace_run, against the plain implementation.
+
+Cuttings: each request whole; most of it in one step and the last 32 tokens one by
+one; portions of changing size down to two tokens; up to four live requests mixed,
+portions of some beside decoded tokens of others, with a pool so small that pages
+are used again.
+"""
+import numpy as np
+import pytest
+import torch
+
+import helpers
+
+pytestmark = pytest.mark.gpu
+
+LENS = [40, 33, 50, 60, 97, 130, 25, 64]
+MAX_TOKENS = 256
+TOL = {"float32": 1e-4, "bfloat16": None}       # bfloat16: relative to the size of the logits, see below
+
+
+def requests_for(cfg):
+    return {f"r{i}": helpers.random_tokens(cfg.vocab_size, n, 100 + i) for i, n in enumerate(LENS)}
+
+
+def make_runner(model_dir, page, dtype, cuda_kernels, max_tokens=MAX_TOKENS):
+    from inferflux_b200.engine import ModelRunner
+    from inferflux_b200.models import load_model
+    _cfg, model = load_model(model_dir, dtype=dtype, device="cuda:0")
+    return ModelRunner(model, cuda_kernels, page_size=page, num_pages=max_tokens // page, max_seqs=8)
+
+
+def check(got, want, dtype, what):
+    if dtype == "float32":
+        bad = helpers.first_bad(got, want, 1e-4)
+        assert bad is None, f"{what}: first wrong row (request, position, diff) = {bad}"
+    else:
+        # bfloat16 keeps 8 bits: activations are rounded at every stage, so rows differ from the
+        # float64 oracle by a few 2^-8 of the logits' scale.  The bound is fixed, not fitted per case.
+        scale = max(float(np.abs(w).max()) for w in want.values())
+        bad = helpers.first_bad(got, want, 0.03 * scale)
+        assert bad is None, f"{what}: first wrong row (request, position, diff) = {bad}, scale {scale}"
+        mean = np.mean([np.abs(got[r] - want[r]).mean() for r in want])
+        assert mean < 0.006 * scale, f"{what}: mean error {mean} at scale {scale}"
+
+
+@pytest.fixture(scope="module")
+def oracle(model_dirs, tiny_configs):
+    out = {}
+    for name, (d, _page) in model_dirs.items():
+        reqs = requests_for(tiny_configs[name][0])
+        out[name] = {"float32": helpers.plain_logits(d, reqs),
+                     "bfloat16": helpers.plain_logits(d, reqs, weights_as=torch.bfloat16)}
+    return out
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("cutting", ["whole", "tail", "portions", "mixed"])
+def test_step_function_cuttings(name, dtype, cutting, model_dirs, tiny_configs, oracle, cuda_kernels):
+    cfg, page = tiny_configs[name]
+    d, _ = model_dirs[name]
+    reqs = requests_for(cfg)
+    steps = {"whole": helpers.trace_whole, "tail": helpers.trace_tail, "portions": helpers.trace_portions,
+             "mixed": lambda r: helpers.trace_mixed(r, MAX_TOKENS)}[cutting](reqs)
+    runner = make_runner(d, page, dtype, cuda_kernels)
+    outputs = helpers.run_steps_in_process(runner, steps)
+    got = helpers.collect(steps, outputs, cfg.vocab_size)
+    check(got, oracle[name][dtype], dtype, f"{name}/{dtype}/{cutting}")
+    assert not runner.cache.live_requests()
+    if cutting == "mixed":
+        g0 = runner.cache.stats()["groups"][0]
+        assert g0["allocations"] > g0["pages"], "the pool was large enough that no page was used again"
+        assert g0["free"] == g0["pages"]
+
+
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_float32_is_the_same_under_every_cutting(name, model_dirs, tiny_configs, cuda_kernels):
+    """The 32-bit kernels add in an order that depends on the position only, so
+    every cutting gives the same bits."""
+    cfg, page = tiny_configs[name]
+    d, _ = model_dirs[name]
+    reqs = requests_for(cfg)
+    results = []
+    for make in (helpers.trace_whole, helpers.trace_portions, lambda r: helpers.trace_mixed(r, MAX_TOKENS)):
+        steps = make(reqs)
+        runner = make_runner(d, page, "float32", cuda_kernels)
+        results.append(helpers.collect(steps, helpers.run_steps_in_process(runner, steps), cfg.vocab_size))
+    for other in results[1:]:
+        for rid in reqs:
+            assert np.array_equal(results[0][rid], other[rid]), f"request {rid} differs between cuttings"
+
+
+@pytest.mark.parametrize("name,dtype", [("B", "float32"), ("C", "bfloat16"), ("A", "bfloat16")])
+def test_trace_run_program(name, dtype, model_dirs, tiny_configs, oracle, tmp_path):
+    """bin/trace_run as a user calls it: one process, all four cuttings one after the other."""
+    cfg, _page = tiny_configs[name]
+    d, _ = model_dirs[name]
+    reqs = requests_for(cfg)
+    want = oracle[name][dtype]
+    steps, owner = [], []
+    for k, make in enumerate((helpers.trace_whole, helpers.trace_tail, helpers.trace_portions,
+                              lambda r: helpers.trace_mixed(r, MAX_TOKENS))):
+        renamed = {f"{rid}_{k}": toks for rid, toks in reqs.items()}
+        for st in make(renamed):
+            st["step"] = len(steps)
+            steps.append(st)
+    outputs = helpers.run_trace_cli(d, dtype, steps, tmp_path / "out", MAX_TOKENS, cfg.vocab_size)
+    got = helpers.collect(steps, outputs, cfg.vocab_size)
+    for k in range(4):
+        part = {rid: got[f"{rid}_{k}"] for rid in reqs}
+        check(part, want, dtype, f"trace_run {name}/{dtype}/cutting {k}")
+
+
+def test_trace_run_refuses_a_bad_model(tmp_path):
+    import json, subprocess, sys
+    (tmp_path / "config.json").write_text(json.dumps({"architectures": ["NoSuchModel"], "model_type": "nosuch"}))
+    proc = subprocess.run([sys.executable, str(helpers.ROOT / "bin" / "trace_run"), "--model", str(tmp_path),
+                           "--dtype", "float32", "--out", str(tmp_path / "o"), "--max-tokens", "64"],
+                          input="", capture_output=True, text=True, timeout=300)
+    assert proc.returncode != 0
+    assert "unsupported architecture" in proc.stderr
