@@ -11,6 +11,9 @@
 // result at a position is bit-for-bit the same however the tokens were cut into
 // steps or batched.
 //
+// `rows`, if given, lists the flat token indices to work on (num_tokens of them);
+// otherwise all tokens 0 .. num_tokens - 1 are done.
+//
 // Head sizes: multiples of 8 up to 256.
 #include "common.cuh"
 
@@ -56,13 +59,14 @@ template <typename T>
 __global__ void attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ kv_pool,
                                          const int* __restrict__ block_table, const int* __restrict__ positions,
                                          const int* __restrict__ token_req, const int* __restrict__ req_slot,
-                                         T* __restrict__ out, int num_tokens, int nq, int nkv, int d,
+                                         const int* __restrict__ rows, T* __restrict__ out, int num_tokens, int nq,
+                                         int nkv, int d,
                                          int page_size, int max_blocks, int num_pages, int window, float scale) {
   __shared__ __align__(16) float q_s[kWarpsPerBlock][kMaxHeadDim];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const long long item = (long long)blockIdx.x * kWarpsPerBlock + warp;
   if (item >= (long long)num_tokens * nq) return;
-  const int t = (int)(item / nq), h = (int)(item % nq);
+  const int t = rows ? rows[item / nq] : (int)(item / nq), h = (int)(item % nq);
   const int g = h / (nq / nkv);
   const int pos = positions[t];
   const int slot = req_slot[token_req[t]];
@@ -129,7 +133,7 @@ using namespace ifx;
 
 extern "C" int ifx_attention_generic(const void* q, const void* kv_pool, const int* block_table,
                                      const int* positions, const int* token_req, const int* req_slot,
-                                     void* out, int num_tokens, int nq, int nkv, int d, int page_size,
+                                     const int* rows, void* out, int num_tokens, int nq, int nkv, int d, int page_size,
                                      int max_blocks, int num_pages, int window, float scale, int dtype,
                                      cudaStream_t stream) {
   if (num_tokens <= 0) return 0;
@@ -139,12 +143,12 @@ extern "C" int ifx_attention_generic(const void* q, const void* kv_pool, const i
   const unsigned blocks = (unsigned)((items + kWarpsPerBlock - 1) / kWarpsPerBlock);
   if (dtype == IFX_DT_F32)
     attention_generic_kernel<float><<<blocks, kWarpsPerBlock * 32, 0, stream>>>(
-        (const float*)q, (const float*)kv_pool, block_table, positions, token_req, req_slot, (float*)out,
+        (const float*)q, (const float*)kv_pool, block_table, positions, token_req, req_slot, rows, (float*)out,
         num_tokens, nq, nkv, d, page_size, max_blocks, num_pages, window, scale);
   else if (dtype == IFX_DT_BF16)
     attention_generic_kernel<__nv_bfloat16><<<blocks, kWarpsPerBlock * 32, 0, stream>>>(
         (const __nv_bfloat16*)q, (const __nv_bfloat16*)kv_pool, block_table, positions, token_req, req_slot,
-        (__nv_bfloat16*)out, num_tokens, nq, nkv, d, page_size, max_blocks, num_pages, window, scale);
+        rows, (__nv_bfloat16*)out, num_tokens, nq, nkv, d, page_size, max_blocks, num_pages, window, scale);
   else
     return IFX_E_DTYPE;
   IFX_CHECK_LAUNCH();

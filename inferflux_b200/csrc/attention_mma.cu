@@ -1,0 +1,585 @@
+// Tiled bfloat16 attention over the paged cache on the warp-level tensor-core path
+// (mma.sync m16n8k16, ldmatrix, cp.async): one kernel for prompt portions and one,
+// with the key range split over thread blocks, for single decoded tokens.
+//
+// Both read keys and values through the block table, page by page, into shared
+// memory whose rows are padded by 16 bytes so that ldmatrix reads are free of bank
+// conflicts.  Scores, the running maximum and sum, and the output accumulate in
+// float32; the softmax works in the log2 domain (scores are multiplied by
+// scale * log2(e) once, then exp2f).
+//
+// Prompt portions: a thread block takes a tile of up to 64 query tokens of one
+// query head; each of its 4 warps owns 16 query rows; key/value tiles of 64 keys
+// are double-buffered.  The keys a row may see are [max(0, pos - window + 1), pos].
+//
+// Decoded tokens: a thread block takes one token, one key/value head and one
+// split of the key range.  The query heads that share the key/value head (up to
+// 16) are the 16 rows of the MMA tile, so every key and value is read once for all
+// of them.  Each warp walks its own 16-key tiles through a 3-stage cp.async
+// pipeline; the warps' partial results are merged in shared memory, and when the
+// key range is split over several blocks each writes (maximum, sum, unnormalised
+// output) to a scratch buffer that a second kernel merges.
+//
+// Head sizes: 16, 32, 48, 64, 80, 96, 112, 128 and 256.  Others, and query groups
+// larger than 16 in decoding, are refused (the caller then uses the generic kernel).
+#include "common.cuh"
+
+namespace ifx {
+
+typedef __nv_bfloat16 bf16;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory");
+}
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+struct PageMap {
+  const int* table;      // this request's row of the block table
+  int page_size, page_shift, num_pages, nkv, g;
+  // Element offset of key `k`'s row (head g) in the pool; the value row lies v_off further.
+  __device__ __forceinline__ size_t key_row(int k, int d) const {
+    int blk, off;
+    if (page_shift >= 0) {
+      blk = k >> page_shift;
+      off = k & (page_size - 1);
+    } else {
+      blk = k / page_size;
+      off = k - blk * page_size;
+    }
+    int page = table[blk];
+    if (page < 0 || page >= num_pages) page = 0;          // a broken table must not leave the pool
+    return ((((size_t)page * 2) * nkv + g) * page_size + off) * d;
+  }
+};
+
+// ------------------------------------------------------------- prompt portions
+template <int D>
+__global__ void __launch_bounds__(128)
+attn_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kv_pool, const int* __restrict__ block_table,
+                    const int* __restrict__ tiles, const int* __restrict__ req_slot, bf16* __restrict__ out, int nq,
+                    int nkv, int page_size, int page_shift, int max_blocks, int num_pages, int window,
+                    float scale_log2) {
+  constexpr int LDS = D + 8;            // shared-memory row stride in elements
+  constexpr int CPR = D / 8;            // 16-byte chunks per row
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  bf16* q_s = reinterpret_cast<bf16*>(smem_raw);        // [64][LDS]
+  bf16* k_s = q_s + 64 * LDS;                           // [2][64][LDS]
+  bf16* v_s = k_s + 2 * 64 * LDS;                       // [2][64][LDS]
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int* tile = tiles + (size_t)blockIdx.x * 4;
+  const int r = tile[0], row0 = tile[1], rows = tile[2], pos0 = tile[3];
+  const int h = blockIdx.y;
+  PageMap pm{block_table + (size_t)req_slot[r] * max_blocks, page_size, page_shift, num_pages, nkv, h / (nq / nkv)};
+  const size_t v_off = (size_t)nkv * page_size * D;
+
+  const int kfirst = window > 0 ? max(0, pos0 - window + 1) : 0;
+  const int kend = pos0 + rows;
+  const int tile_begin = kfirst >> 6, tile_end = (kend + 63) >> 6;
+
+  for (int i = tid; i < 64 * CPR; i += 128) {
+    const int row = i / CPR, c = i % CPR;
+    bf16* dst = q_s + row * LDS + c * 8;
+    if (row < rows)
+      cp_async16(smem_u32(dst), q + ((size_t)(row0 + row) * nq + h) * D + c * 8);
+    else
+      *reinterpret_cast<uint4*>(dst) = make_uint4(0u, 0u, 0u, 0u);
+  }
+  auto load_tile = [&](int t, int stage) {
+    for (int i = tid; i < 64 * CPR; i += 128) {
+      const int row = i / CPR, c = i % CPR;
+      const int k = t * 64 + row;
+      bf16* kd = k_s + (stage * 64 + row) * LDS + c * 8;
+      bf16* vd = v_s + (stage * 64 + row) * LDS + c * 8;
+      if (k >= kfirst && k < kend) {
+        const bf16* src = kv_pool + pm.key_row(k, D) + c * 8;
+        cp_async16(smem_u32(kd), src);
+        cp_async16(smem_u32(vd), src + v_off);
+      } else {                                              // never multiply by whatever lies there
+        *reinterpret_cast<uint4*>(kd) = make_uint4(0u, 0u, 0u, 0u);
+        *reinterpret_cast<uint4*>(vd) = make_uint4(0u, 0u, 0u, 0u);
+      }
+    }
+  };
+  load_tile(tile_begin, 0);
+  cp_async_commit();
+
+  uint32_t qf[D / 16][4];
+  float o[D / 8][4];
+#pragma unroll
+  for (int i = 0; i < D / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
+  float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.0f, l_hi = 0.0f;
+  const int p_lo = pos0 + warp * 16 + (lane >> 2), p_hi = p_lo + 8;
+  const int w_lo = window > 0 ? p_lo - window + 1 : 0, w_hi = window > 0 ? p_hi - window + 1 : 0;
+
+  for (int t = tile_begin; t < tile_end; ++t) {
+    const int stage = (t - tile_begin) & 1;
+    if (t + 1 < tile_end) load_tile(t + 1, stage ^ 1);
+    cp_async_commit();
+    cp_async_wait<1>();
+    __syncthreads();
+    if (t == tile_begin) {
+#pragma unroll
+      for (int kk = 0; kk < D / 16; ++kk) {
+        const int row = warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, col = kk * 16 + (lane >> 4) * 8;
+        ldmatrix_x4(qf[kk], smem_u32(q_s + row * LDS + col));
+      }
+    }
+    const bf16* kt = k_s + stage * 64 * LDS;
+    const bf16* vt = v_s + stage * 64 * LDS;
+    float s[8][4];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.0f;
+#pragma unroll
+    for (int kk = 0; kk < D / 16; ++kk) {
+#pragma unroll
+      for (int n2 = 0; n2 < 4; ++n2) {
+        uint32_t b[4];
+        const int row = n2 * 16 + (lane >> 4) * 8 + (lane & 7), col = kk * 16 + ((lane >> 3) & 1) * 8;
+        ldmatrix_x4(b, smem_u32(kt + row * LDS + col));
+        mma_bf16(s[2 * n2], qf[kk], b[0], b[1]);
+        mma_bf16(s[2 * n2 + 1], qf[kk], b[2], b[3]);
+      }
+    }
+    // mask, scale, running maximum
+    float mx_lo = -INFINITY, mx_hi = -INFINITY;
+#pragma unroll
+    for (int n = 0; n < 8; ++n) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int key = t * 64 + n * 8 + 2 * (lane & 3) + (e & 1);
+        const bool ok = e < 2 ? (key <= p_lo && key >= w_lo) : (key <= p_hi && key >= w_hi);
+        s[n][e] = ok ? s[n][e] * scale_log2 : -INFINITY;
+      }
+      mx_lo = fmaxf(mx_lo, fmaxf(s[n][0], s[n][1]));
+      mx_hi = fmaxf(mx_hi, fmaxf(s[n][2], s[n][3]));
+    }
+    mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1));
+    mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
+    mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1));
+    mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
+    const float mn_lo = fmaxf(m_lo, mx_lo), mn_hi = fmaxf(m_hi, mx_hi);
+    const float mu_lo = mn_lo == -INFINITY ? 0.0f : mn_lo, mu_hi = mn_hi == -INFINITY ? 0.0f : mn_hi;
+    const float c_lo = exp2f(m_lo - mu_lo), c_hi = exp2f(m_hi - mu_hi);
+    m_lo = mn_lo;
+    m_hi = mn_hi;
+    l_lo *= c_lo;
+    l_hi *= c_hi;
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i) {
+      o[i][0] *= c_lo;
+      o[i][1] *= c_lo;
+      o[i][2] *= c_hi;
+      o[i][3] *= c_hi;
+    }
+    uint32_t pa[4][4];
+#pragma unroll
+    for (int n = 0; n < 8; ++n) {
+      const float e0 = exp2f(s[n][0] - mu_lo), e1 = exp2f(s[n][1] - mu_lo);
+      const float e2 = exp2f(s[n][2] - mu_hi), e3 = exp2f(s[n][3] - mu_hi);
+      l_lo += e0 + e1;
+      l_hi += e2 + e3;
+      pa[n >> 1][(n & 1) * 2] = pack_bf16(e0, e1);
+      pa[n >> 1][(n & 1) * 2 + 1] = pack_bf16(e2, e3);
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+#pragma unroll
+      for (int d2 = 0; d2 < D / 16; ++d2) {
+        uint32_t b[4];
+        const int row = j * 16 + ((lane >> 3) & 1) * 8 + (lane & 7), col = d2 * 16 + (lane >> 4) * 8;
+        ldmatrix_x4_trans(b, smem_u32(vt + row * LDS + col));
+        mma_bf16(o[2 * d2], pa[j], b[0], b[1]);
+        mma_bf16(o[2 * d2 + 1], pa[j], b[2], b[3]);
+      }
+    }
+    __syncthreads();
+  }
+  l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1);
+  l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
+  l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1);
+  l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
+  const float i_lo = l_lo > 0.0f ? 1.0f / l_lo : 0.0f, i_hi = l_hi > 0.0f ? 1.0f / l_hi : 0.0f;
+  const int r_lo = warp * 16 + (lane >> 2), r_hi = r_lo + 8;
+#pragma unroll
+  for (int n = 0; n < D / 8; ++n) {
+    const int col = n * 8 + 2 * (lane & 3);
+    if (r_lo < rows)
+      *reinterpret_cast<uint32_t*>(out + ((size_t)(row0 + r_lo) * nq + h) * D + col) =
+          pack_bf16(o[n][0] * i_lo, o[n][1] * i_lo);
+    if (r_hi < rows)
+      *reinterpret_cast<uint32_t*>(out + ((size_t)(row0 + r_hi) * nq + h) * D + col) =
+          pack_bf16(o[n][2] * i_hi, o[n][3] * i_hi);
+  }
+}
+
+// -------------------------------------------------------------- decoded tokens
+template <int D, int STAGES>
+__global__ void __launch_bounds__(128)
+attn_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kv_pool, const int* __restrict__ block_table,
+                   const int* __restrict__ decode_rows, const int* __restrict__ positions,
+                   const int* __restrict__ token_req, const int* __restrict__ req_slot, float* __restrict__ part_o,
+                   float* __restrict__ part_ml, bf16* __restrict__ out, int nq, int nkv, int page_size, int page_shift,
+                   int max_blocks, int num_pages, int window, float scale_log2, int num_splits) {
+  constexpr int LDS = D + 8;
+  constexpr int CPR = D / 8;
+  constexpr int STAGE_ELEMS = 2 * 16 * LDS;             // K tile then V tile
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  bf16* q_s = reinterpret_cast<bf16*>(smem_raw);        // [16][LDS]
+  bf16* stage_base = q_s + 16 * LDS;                    // [4 warps][STAGES][2][16][LDS]
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int item = blockIdx.x, g = blockIdx.y, split = blockIdx.z;
+  const int G = nq / nkv;
+  const int t = decode_rows[item];
+  const int pos = positions[t];
+  PageMap pm{block_table + (size_t)req_slot[token_req[t]] * max_blocks, page_size, page_shift, num_pages, nkv, g};
+  const size_t v_off = (size_t)nkv * page_size * D;
+
+  const int kfirst = window > 0 ? max(0, pos - window + 1) : 0;
+  const int kend = pos + 1;
+  const int per_split = (((kend - kfirst + num_splits - 1) / num_splits) + 63) / 64 * 64;
+  const int k0 = kfirst + split * per_split;
+  const int k1 = min(kend, k0 + per_split);
+
+  for (int i = tid; i < 16 * CPR; i += 128) {
+    const int row = i / CPR, c = i % CPR;
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (row < G) v = *reinterpret_cast<const uint4*>(q + ((size_t)t * nq + g * G + row) * D + c * 8);
+    *reinterpret_cast<uint4*>(q_s + row * LDS + c * 8) = v;
+  }
+  __syncthreads();
+  uint32_t qf[D / 16][4];
+#pragma unroll
+  for (int kk = 0; kk < D / 16; ++kk) {
+    const int row = (lane & 7) + ((lane >> 3) & 1) * 8, col = kk * 16 + (lane >> 4) * 8;
+    ldmatrix_x4(qf[kk], smem_u32(q_s + row * LDS + col));
+  }
+
+  bf16* my_stages = stage_base + (size_t)warp * STAGES * STAGE_ELEMS;
+  auto load_tile = [&](int base, int stage) {            // keys base .. base + 15 of this warp
+    bf16* kd0 = my_stages + stage * STAGE_ELEMS;
+    for (int i = lane; i < 16 * CPR; i += 32) {
+      const int row = i / CPR, c = i % CPR;
+      const int k = base + row;
+      bf16* kd = kd0 + row * LDS + c * 8;
+      bf16* vd = kd + 16 * LDS;
+      if (k < k1) {
+        const bf16* src = kv_pool + pm.key_row(k, D) + c * 8;
+        cp_async16(smem_u32(kd), src);
+        cp_async16(smem_u32(vd), src + v_off);
+      } else {
+        *reinterpret_cast<uint4*>(kd) = make_uint4(0u, 0u, 0u, 0u);
+        *reinterpret_cast<uint4*>(vd) = make_uint4(0u, 0u, 0u, 0u);
+      }
+    }
+  };
+
+  float o[D / 8][4];
+#pragma unroll
+  for (int i = 0; i < D / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
+  float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.0f, l_hi = 0.0f;
+
+  const int first_base = k0 + warp * 16;
+  const int stride = 64;
+#pragma unroll
+  for (int s = 0; s < STAGES - 1; ++s) {
+    if (first_base + s * stride < k1) load_tile(first_base + s * stride, s);
+    cp_async_commit();
+  }
+  int n_iter = 0;
+  for (int base = first_base; base < k1; base += stride, ++n_iter) {
+    const int ahead = base + (STAGES - 1) * stride;
+    if (ahead < k1) load_tile(ahead, (n_iter + STAGES - 1) % STAGES);
+    cp_async_commit();
+    cp_async_wait<STAGES - 1>();
+    __syncwarp();
+    const bf16* kt = my_stages + (n_iter % STAGES) * STAGE_ELEMS;
+    const bf16* vt = kt + 16 * LDS;
+    float s[2][4];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.0f;
+#pragma unroll
+    for (int kk = 0; kk < D / 16; ++kk) {
+      uint32_t b[4];
+      const int row = (lane >> 4) * 8 + (lane & 7), col = kk * 16 + ((lane >> 3) & 1) * 8;
+      ldmatrix_x4(b, smem_u32(kt + row * LDS + col));
+      mma_bf16(s[0], qf[kk], b[0], b[1]);
+      mma_bf16(s[1], qf[kk], b[2], b[3]);
+    }
+    float mx_lo = -INFINITY, mx_hi = -INFINITY;
+#pragma unroll
+    for (int n = 0; n < 2; ++n) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int key = base + n * 8 + 2 * (lane & 3) + (e & 1);
+        s[n][e] = key < k1 ? s[n][e] * scale_log2 : -INFINITY;
+      }
+      mx_lo = fmaxf(mx_lo, fmaxf(s[n][0], s[n][1]));
+      mx_hi = fmaxf(mx_hi, fmaxf(s[n][2], s[n][3]));
+    }
+    mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1));
+    mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
+    mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1));
+    mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
+    const float mn_lo = fmaxf(m_lo, mx_lo), mn_hi = fmaxf(m_hi, mx_hi);   // finite: key `base` is always valid
+    const float c_lo = exp2f(m_lo - mn_lo), c_hi = exp2f(m_hi - mn_hi);
+    m_lo = mn_lo;
+    m_hi = mn_hi;
+    l_lo *= c_lo;
+    l_hi *= c_hi;
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i) {
+      o[i][0] *= c_lo;
+      o[i][1] *= c_lo;
+      o[i][2] *= c_hi;
+      o[i][3] *= c_hi;
+    }
+    uint32_t pa[4];
+    {
+      const float e0 = exp2f(s[0][0] - mn_lo), e1 = exp2f(s[0][1] - mn_lo);
+      const float e2 = exp2f(s[0][2] - mn_hi), e3 = exp2f(s[0][3] - mn_hi);
+      const float f0 = exp2f(s[1][0] - mn_lo), f1 = exp2f(s[1][1] - mn_lo);
+      const float f2 = exp2f(s[1][2] - mn_hi), f3 = exp2f(s[1][3] - mn_hi);
+      l_lo += e0 + e1 + f0 + f1;
+      l_hi += e2 + e3 + f2 + f3;
+      pa[0] = pack_bf16(e0, e1);
+      pa[1] = pack_bf16(e2, e3);
+      pa[2] = pack_bf16(f0, f1);
+      pa[3] = pack_bf16(f2, f3);
+    }
+#pragma unroll
+    for (int d2 = 0; d2 < D / 16; ++d2) {
+      uint32_t b[4];
+      const int row = ((lane >> 3) & 1) * 8 + (lane & 7), col = d2 * 16 + (lane >> 4) * 8;
+      ldmatrix_x4_trans(b, smem_u32(vt + row * LDS + col));
+      mma_bf16(o[2 * d2], pa, b[0], b[1]);
+      mma_bf16(o[2 * d2 + 1], pa, b[2], b[3]);
+    }
+    __syncwarp();
+  }
+  cp_async_wait<0>();
+  l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1);
+  l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
+  l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1);
+  l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
+
+  // ---- merge the four warps in shared memory (the staging buffers are free now)
+  __syncthreads();
+  float* c_o = reinterpret_cast<float*>(stage_base);          // [4][16][D]
+  float* c_m = c_o + 4 * 16 * D;                              // [4][16]
+  float* c_l = c_m + 4 * 16;                                  // [4][16]
+  {
+    const int r_lo = lane >> 2, r_hi = r_lo + 8;
+#pragma unroll
+    for (int n = 0; n < D / 8; ++n) {
+      const int col = n * 8 + 2 * (lane & 3);
+      c_o[(warp * 16 + r_lo) * D + col] = o[n][0];
+      c_o[(warp * 16 + r_lo) * D + col + 1] = o[n][1];
+      c_o[(warp * 16 + r_hi) * D + col] = o[n][2];
+      c_o[(warp * 16 + r_hi) * D + col + 1] = o[n][3];
+    }
+    if ((lane & 3) == 0) {
+      c_m[warp * 16 + r_lo] = m_lo;
+      c_m[warp * 16 + r_hi] = m_hi;
+      c_l[warp * 16 + r_lo] = l_lo;
+      c_l[warp * 16 + r_hi] = l_hi;
+    }
+  }
+  __syncthreads();
+  for (int idx = tid; idx < G * D; idx += 128) {
+    const int row = idx / D, dim = idx % D;
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) M = fmaxf(M, c_m[w * 16 + row]);
+    float O = 0.0f, L = 0.0f;
+    if (M != -INFINITY) {
+#pragma unroll
+      for (int w = 0; w < 4; ++w) {
+        const float f = exp2f(c_m[w * 16 + row] - M);
+        O += f * c_o[(w * 16 + row) * D + dim];
+        L += f * c_l[w * 16 + row];
+      }
+    }
+    const int head = g * G + row;
+    if (num_splits == 1) {
+      out[((size_t)t * nq + head) * D + dim] = __float2bfloat16_rn(L > 0.0f ? O / L : 0.0f);
+    } else {
+      const size_t p = ((size_t)item * nq + head) * num_splits + split;
+      part_o[p * D + dim] = O;
+      if (dim == 0) {
+        part_ml[p * 2] = M;
+        part_ml[p * 2 + 1] = L;
+      }
+    }
+  }
+}
+
+// Merge of the splits: out = sum_s 2^(m_s - M) O_s / sum_s 2^(m_s - M) l_s.
+__global__ void attn_decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                         const int* __restrict__ decode_rows, bf16* __restrict__ out, int nq, int d,
+                                         int num_splits) {
+  const int item = blockIdx.x, head = blockIdx.y;
+  const size_t p0 = ((size_t)item * nq + head) * num_splits;
+  float M = -INFINITY;
+  for (int s = 0; s < num_splits; ++s) M = fmaxf(M, part_ml[(p0 + s) * 2]);
+  const int t = decode_rows[item];
+  for (int dim = threadIdx.x; dim < d; dim += blockDim.x) {
+    float O = 0.0f, L = 0.0f;
+    if (M != -INFINITY) {
+      for (int s = 0; s < num_splits; ++s) {
+        const float f = exp2f(part_ml[(p0 + s) * 2] - M);
+        O += f * part_o[(p0 + s) * d + dim];
+        L += f * part_ml[(p0 + s) * 2 + 1];
+      }
+    }
+    out[((size_t)t * nq + head) * d + dim] = __float2bfloat16_rn(L > 0.0f ? O / L : 0.0f);
+  }
+}
+
+template <int D>
+int launch_prefill(const bf16* q, const bf16* kv_pool, const int* block_table, const int* tiles, const int* req_slot,
+                   bf16* out, int num_tiles, int nq, int nkv, int page_size, int page_shift, int max_blocks,
+                   int num_pages, int window, float scale_log2, cudaStream_t stream) {
+  constexpr int smem = (64 + 4 * 64) * (D + 8) * 2;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  dim3 grid(num_tiles, nq);
+  attn_prefill_kernel<D><<<grid, 128, smem, stream>>>(q, kv_pool, block_table, tiles, req_slot, out, nq, nkv, page_size,
+                                                      page_shift, max_blocks, num_pages, window, scale_log2);
+  IFX_CHECK_LAUNCH();
+  return 0;
+}
+
+template <int D>
+int launch_decode(const bf16* q, const bf16* kv_pool, const int* block_table, const int* decode_rows,
+                  const int* positions, const int* token_req, const int* req_slot, float* part_o, float* part_ml,
+                  bf16* out, int num_items, int nq, int nkv, int page_size, int page_shift, int max_blocks,
+                  int num_pages, int window, float scale_log2, int num_splits, cudaStream_t stream) {
+  constexpr int STAGES = D <= 128 ? 3 : 2;
+  constexpr int stage_bytes = 4 * STAGES * 2 * 16 * (D + 8) * 2;
+  constexpr int merge_bytes = (4 * 16 * D + 2 * 4 * 16) * 4;
+  constexpr int smem = 16 * (D + 8) * 2 + (stage_bytes > merge_bytes ? stage_bytes : merge_bytes);
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<D, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         smem);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  dim3 grid(num_items, nkv, num_splits);
+  attn_decode_kernel<D, STAGES><<<grid, 128, smem, stream>>>(q, kv_pool, block_table, decode_rows, positions, token_req,
+                                                             req_slot, part_o, part_ml, out, nq, nkv, page_size,
+                                                             page_shift, max_blocks, num_pages, window, scale_log2,
+                                                             num_splits);
+  IFX_CHECK_LAUNCH();
+  if (num_splits > 1) {
+    dim3 mgrid(num_items, nq);
+    attn_decode_merge_kernel<<<mgrid, D >= 128 ? 128 : 64, 0, stream>>>(part_o, part_ml, decode_rows, out, nq, D,
+                                                                        num_splits);
+    IFX_CHECK_LAUNCH();
+  }
+  return 0;
+}
+
+static int shift_of(int page_size) {
+  if (page_size <= 0 || (page_size & (page_size - 1))) return -1;
+  int s = 0;
+  while ((1 << s) < page_size) ++s;
+  return s;
+}
+
+}  // namespace ifx
+
+using namespace ifx;
+
+#define IFX_DISPATCH_D(d, CALL)                    \
+  switch (d) {                                     \
+    case 16: return CALL(16);                      \
+    case 32: return CALL(32);                      \
+    case 48: return CALL(48);                      \
+    case 64: return CALL(64);                      \
+    case 80: return CALL(80);                      \
+    case 96: return CALL(96);                      \
+    case 112: return CALL(112);                    \
+    case 128: return CALL(128);                    \
+    case 256: return CALL(256);                    \
+    default: return IFX_E_BADARG;                  \
+  }
+
+extern "C" {
+
+// 1 if the tiled kernels take this head size, else 0.
+int ifx_attention_mma_supports(int d) {
+  return d == 16 || d == 32 || d == 48 || d == 64 || d == 80 || d == 96 || d == 112 || d == 128 || d == 256;
+}
+
+// tiles: int32 [num_tiles, 4] = (request index, first flat row, rows <= 64, first position).
+int ifx_attention_prefill_bf16(const void* q, const void* kv_pool, const int* block_table, const int* tiles,
+                               const int* req_slot, void* out, int num_tiles, int nq, int nkv, int d, int page_size,
+                               int max_blocks, int num_pages, int window, float scale, cudaStream_t stream) {
+  if (num_tiles <= 0) return 0;
+  if (nq <= 0 || nkv <= 0 || nq % nkv || page_size <= 0 || max_blocks <= 0 || nq > 65535) return IFX_E_BADARG;
+  const float scale_log2 = scale * 1.4426950408889634f;
+  const int ps = shift_of(page_size);
+#define CALL(DD)                                                                                                   \
+  launch_prefill<DD>((const bf16*)q, (const bf16*)kv_pool, block_table, tiles, req_slot, (bf16*)out, num_tiles, nq, \
+                     nkv, page_size, ps, max_blocks, num_pages, window, scale_log2, stream)
+  IFX_DISPATCH_D(d, CALL)
+#undef CALL
+}
+
+// part_o: float32 [num_items, nq, num_splits, d]; part_ml: float32 [num_items, nq, num_splits, 2]
+// (both unused when num_splits == 1).
+int ifx_attention_decode_bf16(const void* q, const void* kv_pool, const int* block_table, const int* decode_rows,
+                              const int* positions, const int* token_req, const int* req_slot, float* part_o,
+                              float* part_ml, void* out, int num_items, int nq, int nkv, int d, int page_size,
+                              int max_blocks, int num_pages, int window, float scale, int num_splits,
+                              cudaStream_t stream) {
+  if (num_items <= 0) return 0;
+  if (nq <= 0 || nkv <= 0 || nq % nkv || nq / nkv > 16 || page_size <= 0 || max_blocks <= 0 || num_splits <= 0 ||
+      nkv > 65535 || num_splits > 65535 || nq > 65535)
+    return IFX_E_BADARG;
+  if (num_splits > 1 && (part_o == nullptr || part_ml == nullptr)) return IFX_E_BADARG;
+  const float scale_log2 = scale * 1.4426950408889634f;
+  const int ps = shift_of(page_size);
+#define CALL(DD)                                                                                                     \
+  launch_decode<DD>((const bf16*)q, (const bf16*)kv_pool, block_table, decode_rows, positions, token_req, req_slot,  \
+                    part_o, part_ml, (bf16*)out, num_items, nq, nkv, page_size, ps, max_blocks, num_pages, window,   \
+                    scale_log2, num_splits, stream)
+  IFX_DISPATCH_D(d, CALL)
+#undef CALL
+}
+
+}  // extern "C"

@@ -61,7 +61,8 @@ class CudaKernels:
         for fn in ("ifx_embed", "ifx_rmsnorm", "ifx_silu_mul", "ifx_residual_add", "ifx_gather_rows",
                    "ifx_scatter_i32", "ifx_rope_append", "ifx_attention_generic", "ifx_gemm_generic",
                    "ifx_gemm_cublas_bf16", "ifx_cublas_init", "ifx_argmax", "ifx_penalties", "ifx_logit_bias",
-                   "ifx_sample"):
+                   "ifx_sample", "ifx_attention_mma_supports", "ifx_attention_prefill_bf16",
+                   "ifx_attention_decode_bf16"):
             getattr(self.lib, fn).restype = ctypes.c_int
         with torch.cuda.device(self.device):
             _check(self.lib.ifx_cublas_init(), "cublas init")
@@ -179,18 +180,56 @@ class CudaKernels:
         return q_out
 
     def attention(self, q, nq, nkv, d, window, scale, ctx, cache):
+        """Every token attends its request's keys up to its own position (or the last
+        `window` of them) through the block table.  float32: the per-token kernel
+        whose additions depend on the position only.  bfloat16: the tiled kernels,
+        one launch for the prompt portions and one for the single decoded tokens."""
         T = q.shape[0]
         kv, table = cache.kv, cache.block_table
         _need(kv is not None and table is not None, "attention: the mixer has no key/value cache")
         _need(kv.dtype == q.dtype, f"attention: cache is {kv.dtype}, queries {q.dtype}")
         _need(d % 8 == 0 and d <= 256, f"attention: head size {d} is not a multiple of 8 up to 256")
         out = torch.empty((T, nq * d), dtype=q.dtype, device=q.device)
+        win = 0 if window is None else int(window)
+        common = (cache.page_size, table.shape[1], kv.shape[0], win, ctypes.c_float(scale))
+        tiled = q.dtype == torch.bfloat16 and bool(self.lib.ifx_attention_mma_supports(d))
+        if not tiled:
+            self._attention_generic(q, kv, table, ctx, None, T, out, nq, nkv, d, common)
+            return out
+        if ctx.num_prefill_tiles:
+            _check(self.lib.ifx_attention_prefill_bf16(
+                _ptr(q), _ptr(kv), _ptr(table), _ptr(ctx.prefill_tiles), _ptr(ctx.req_slot), _ptr(out),
+                ctx.num_prefill_tiles, nq, nkv, d, *common, _stream()), "attention (prompt portions)")
+            self.launches += 1
+        n = ctx.num_decode_rows
+        if n:
+            if nq // nkv > 16:
+                self._attention_generic(q, kv, table, ctx, ctx.decode_rows, n, out, nq, nkv, d, common)
+                return out
+            splits = self.decode_splits(n, nkv, ctx.max_kv_len if not win else min(win, ctx.max_kv_len))
+            part_o = part_ml = None
+            if splits > 1:
+                part_o = torch.empty((n, nq, splits, d), dtype=torch.float32, device=q.device)
+                part_ml = torch.empty((n, nq, splits, 2), dtype=torch.float32, device=q.device)
+            _check(self.lib.ifx_attention_decode_bf16(
+                _ptr(q), _ptr(kv), _ptr(table), _ptr(ctx.decode_rows), _ptr(ctx.positions), _ptr(ctx.token_req),
+                _ptr(ctx.req_slot), _ptr(part_o), _ptr(part_ml), _ptr(out), n, nq, nkv, d, *common, splits,
+                _stream()), "attention (decoded tokens)")
+            self.launches += 2 if splits > 1 else 1
+        return out
+
+    @staticmethod
+    def decode_splits(num_tokens, nkv, max_keys):
+        """Into how many thread blocks the key range of a decoded token is cut: enough
+        blocks to fill the 148 SMs twice, but at least 128 keys per block."""
+        want = -(-296 // max(1, num_tokens * nkv))
+        return max(1, min(want, max(1, max_keys // 128), 64))
+
+    def _attention_generic(self, q, kv, table, ctx, rows, count, out, nq, nkv, d, common):
         _check(self.lib.ifx_attention_generic(
             _ptr(q), _ptr(kv), _ptr(table), _ptr(ctx.positions), _ptr(ctx.token_req), _ptr(ctx.req_slot),
-            _ptr(out), T, nq, nkv, d, cache.page_size, table.shape[1], kv.shape[0],
-            0 if window is None else int(window), ctypes.c_float(scale), _DT[q.dtype], _stream()), "attention")
+            _ptr(rows), _ptr(out), count, nq, nkv, d, *common, _DT[q.dtype], _stream()), "attention")
         self.launches += 1
-        return out
 
     # ---------------------------------------------------------------- sampling
     def argmax(self, logits):

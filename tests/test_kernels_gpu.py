@@ -123,6 +123,18 @@ def make_cache_case(dtype, nkv, d, page, lens, spans, num_pages, seed, shuffle=T
     ctx.token_req = torch.tensor(token_req, dtype=torch.int32, device=DEV)
     ctx.req_slot = torch.tensor(slots, dtype=torch.int32, device=DEV)
     ctx.num_tokens = len(positions)
+    tiles, decode_rows, base = [], [], 0
+    for r, (n, s_) in enumerate(zip(lens, spans)):
+        if s_ == 1:
+            decode_rows.append(base)
+        else:
+            for off in range(0, s_, 64):
+                tiles.append([r, base + off, min(64, s_ - off), n - s_ + off])
+        base += s_
+    ctx.decode_rows = torch.tensor(decode_rows, dtype=torch.int32, device=DEV)
+    ctx.prefill_tiles = torch.tensor(tiles, dtype=torch.int32, device=DEV).view(-1, 4)
+    ctx.num_decode_rows, ctx.num_prefill_tiles = len(decode_rows), len(tiles)
+    ctx.max_kv_len = max(lens)
     cache = CacheView(kv.to(DEV), table.to(DEV), page, None, True, 0)
     return ctx, cache, slots
 
@@ -161,14 +173,15 @@ def attention_oracle(q, stored, lens, spans, nq, nkv, d, window, scale):
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("nq,nkv,d,page,window", [
     (4, 2, 16, 4, None), (6, 2, 32, 8, None), (7, 1, 128, 16, None), (5, 5, 48, 16, 21),
-    (28, 4, 128, 16, None), (12, 2, 64, 32, 100), (3, 1, 80, 8, 7), (2, 1, 256, 16, None)])
+    (28, 4, 128, 16, None), (12, 2, 64, 32, 100), (3, 1, 80, 8, 7), (2, 1, 256, 16, None),
+    (34, 2, 32, 16, None), (4, 2, 144, 16, None), (8, 1, 96, 5, 33), (6, 3, 112, 64, None)])
 def test_attention_over_pages(cuda_kernels, dtype, nq, nkv, d, page, window):
     """Mixed spans (prompt portions beside single tokens) over shuffled pages, with
     sharp data: one far key per query dominates, so a key that is missed, read from
     the wrong page or masked wrongly changes the result."""
-    lens = [1, 37, 130, 64, 259, 16]
-    spans = [1, 1, 50, 64, 3, 2]
-    ctx, cache, slots = make_cache_case(dtype, nkv, d, page, lens, spans, num_pages=80 if page >= 8 else 200,
+    lens = [1, 37, 130, 64, 259, 16, 1500, 200]
+    spans = [1, 1, 50, 64, 3, 2, 1, 150]
+    ctx, cache, slots = make_cache_case(dtype, nkv, d, page, lens, spans, num_pages=sum(-(-n // page) for n in lens) + 3,
                                         seed=3)
     stored = fill_cache(cache, lens, slots, nkv, d, dtype, seed=4)
     T = ctx.num_tokens
