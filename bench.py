@@ -245,6 +245,7 @@ def main() -> int:
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=0, help="run fewer layers than the 7B shape has (named in config)")
     ap.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64")
+    ap.add_argument("--no-prefill", action="store_true", help="skip the 2,048-token prefill (for profiling decode)")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -279,7 +280,7 @@ def main() -> int:
     step_bytes = weight_bytes(cfg, args.batch) + args.batch * ctx_len * kv_bytes_per_token(cfg)
     achieved = step_bytes / (dev_ms * 1e-3) / 1e9
 
-    prefill_ms = time_prefill(engine, cfg, PREFILL_TOKENS, warmup=3, reps=5)
+    prefill_ms = float("inf") if args.no_prefill else time_prefill(engine, cfg, PREFILL_TOKENS, warmup=3, reps=5)
     pf_flops = prefill_flops(cfg, PREFILL_TOKENS)
     pf_frac = pf_flops / (prefill_ms * 1e-3) / (pk["bf16_tflops"] * 1e12)
 

@@ -105,10 +105,13 @@ class StepContext:
             sections[f"upd_index_{g}"] = [u[0] for u in ups]
             sections[f"upd_page_{g}"] = [u[1] for u in ups]
         offsets, flat = {}, []
+        core_len = 0
         for name, vals in sections.items():
             offsets[name] = (len(flat), len(vals))
             flat.extend(vals)
             flat.extend([0] * ((-len(flat)) % 4))                 # keep every section 16-byte aligned
+            if not name.startswith("upd_"):
+                core_len = len(flat)                              # the updates come last
         host = torch.tensor(flat if flat else [0], dtype=torch.int32)
         if ctx.device.type == "cuda":
             host = host.pin_memory()
@@ -117,9 +120,30 @@ class StepContext:
             dev = host
         ctx._host_buffer = host                                   # keep pinned memory alive until the copy ran
         ctx.meta_bytes = host.numel() * 4
-        for name, (off, n) in offsets.items():
-            setattr(ctx, name, dev[off:off + n])
-        ctx.prefill_tiles = ctx.prefill_tiles.view(-1, 4)
-        ctx.table_updates = [(getattr(ctx, f"upd_index_{g}"), getattr(ctx, f"upd_page_{g}"))
+        ctx._offsets, ctx._core_len, ctx._buffer = offsets, core_len, dev
+        ctx._bind(dev)
+        ctx.table_updates = [(dev[offsets[f"upd_index_{g}"][0]:][:offsets[f"upd_index_{g}"][1]],
+                              dev[offsets[f"upd_page_{g}"][0]:][:offsets[f"upd_page_{g}"][1]])
                              for g in range(len(table_updates))]
         return ctx
+
+    _CORE = ("token_ids", "positions", "token_req", "cu_seqlens", "kv_lens", "req_slot", "logit_rows",
+             "decode_rows", "prefill_tiles")
+
+    def _bind(self, buffer):
+        for name in self._CORE:
+            off, n = self._offsets[name]
+            setattr(self, name, buffer[off:off + n])
+        self.prefill_tiles = self.prefill_tiles.view(-1, 4)
+
+    def layout_key(self):
+        """Two steps with the same key have their arrays at the same offsets."""
+        return tuple(self._offsets[n] for n in self._CORE)
+
+    def core_buffer(self):
+        return self._buffer[:self._core_len]
+
+    def rebind(self, static_buffer):
+        """Point the arrays at `static_buffer` (same layout), e.g. the fixed addresses a
+        captured CUDA graph reads."""
+        self._bind(static_buffer)

@@ -55,7 +55,7 @@ class Engine:
                  kv_max_batch: int = 16, kv_max_seq: Optional[int] = None, kv_budget_mb: Optional[float] = None,
                  kv_budget_ratio: float = 0.20, max_batch_size: int = 32, max_batch_tokens: int = 16384,
                  chunked_prefill_tokens: int = 512, mixed_prefill_budget_ratio: float = 1.0,
-                 sampling_seed: int = 0, loaded_model=None):
+                 sampling_seed: int = 0, cuda_graphs: bool = True, loaded_model=None):
         """`model`: a folder with config.json and model.safetensors.  Without it,
         `config` (a typed configuration) and `seed` make random weights on the device."""
         self.device = torch.device(device)
@@ -80,7 +80,7 @@ class Engine:
         if kv_num_pages is None:
             kv_num_pages = self._plan_pages(kv_page_size, max_seqs, max_seq, kv_budget_mb, kv_budget_ratio)
         self.runner = ModelRunner(self.model, kernels, page_size=kv_page_size, num_pages=kv_num_pages,
-                                  max_seqs=max_seqs, max_seq_len=max_seq)
+                                  max_seqs=max_seqs, max_seq_len=max_seq, cuda_graphs=cuda_graphs)
         self.scheduler = Scheduler(SchedulerConfig(max_batch_size=min(max_batch_size, max_seqs),
                                                    max_batch_tokens=max_batch_tokens,
                                                    chunked_prefill_tokens=chunked_prefill_tokens,

@@ -27,8 +27,11 @@ class StepError(ValueError):
 class ModelRunner:
     """A loaded model, its cache and the kernel table: everything `step` needs."""
 
+    MAX_GRAPHS = 24
+
     def __init__(self, model, kernels, page_size: int = 16, num_pages: int = 256, max_seqs: int = 8,
-                 max_seq_len: Optional[int] = None, cache_dtype: Optional[torch.dtype] = None):
+                 max_seq_len: Optional[int] = None, cache_dtype: Optional[torch.dtype] = None,
+                 cuda_graphs: bool = False):
         self.model = model
         self.kernels = kernels
         self.dtype = model.dtype
@@ -41,6 +44,13 @@ class ModelRunner:
                                   dtype=cache_dtype or model.dtype, device=self.device)
         self.steps = 0
         self.tokens_run = 0
+        # Decode-only steps (one token per request, logits of every token) replay a CUDA graph
+        # captured per (batch size, context bucket), as the reference does per batch size
+        # (runtime/backends/cuda/native/transformer_forward.cu:3071-3101, 4369-4399).
+        self.cuda_graphs = bool(cuda_graphs) and self.device.type == "cuda" and all(
+            p.graph_safe for _n, p in model.named_parts())
+        self._graphs = {}              # key -> [uses, graph or None, static buffer, static logits]
+        self.graph_replays = 0
 
     # ---------------------------------------------------------------- requests
     def add_request(self, rid: Hashable) -> int:
@@ -113,10 +123,44 @@ class ModelRunner:
                                 cache.drain_table_updates())
         for group, (index, page) in zip(cache.groups, ctx.table_updates):
             self.kernels.scatter_i32(group.table, index, page)
-        logits = self.model.forward(ctx, cache)
+        logits = self._forward(ctx, entries)
         for e, start in zip(entries, starts):
             cache.commit(e.request_id, start + len(e.tokens))
         self.steps += 1
         self.tokens_run += ctx.num_tokens
         self.last_ctx = ctx
         return logits
+
+    # ------------------------------------------------------------------ graphs
+    def _forward(self, ctx: StepContext, entries) -> torch.Tensor:
+        if not self.cuda_graphs or ctx.max_span != 1 or ctx.num_logit_rows != ctx.num_tokens:
+            return self.model.forward(ctx, self.cache)
+        bucket = 256
+        while bucket < ctx.max_kv_len:
+            bucket *= 2
+        key = (ctx.num_tokens, bucket, ctx.layout_key())
+        slot = self._graphs.get(key)
+        if slot is None:                                   # first time: run as is (also warms every kernel up)
+            if len(self._graphs) >= self.MAX_GRAPHS:
+                self._graphs.pop(next(iter(self._graphs)))
+            self._graphs[key] = [1, None, None, None]
+            return self.model.forward(ctx, self.cache)
+        slot[0] += 1
+        if slot[1] is None:                                # second time: capture
+            static = torch.empty_like(ctx.core_buffer())
+            static.copy_(ctx.core_buffer())
+            ctx.rebind(static)
+            ctx.max_kv_len = bucket                        # what depends on the context is fixed per bucket
+            torch.cuda.synchronize(self.device)
+            graph = torch.cuda.CUDAGraph()
+            launches = self.kernels.launches
+            with torch.cuda.graph(graph):
+                static_logits = self.model.forward(ctx, self.cache)
+            slot[1], slot[2], slot[3] = graph, static, static_logits
+            slot.append(self.kernels.launches - launches)
+        else:
+            slot[2].copy_(ctx.core_buffer(), non_blocking=True)
+            self.kernels.launches += slot[4]
+        slot[1].replay()
+        self.graph_replays += 1
+        return slot[3].clone()

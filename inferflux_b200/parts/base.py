@@ -58,6 +58,10 @@ class RotaryTable:
 class Part:
     """Base of all parts."""
 
+    # False for a part whose forward reads device data on the host or launches work whose
+    # shape depends on the data: a step that holds such a part is never captured into a CUDA graph.
+    graph_safe = True
+
     def __init__(self, spec: PartSpec):
         self.spec = spec
 

@@ -120,3 +120,21 @@ def test_trace_run_refuses_a_bad_model(tmp_path):
                           input="", capture_output=True, text=True, timeout=300)
     assert proc.returncode != 0
     assert "unsupported architecture" in proc.stderr
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_decode_steps_replayed_from_a_cuda_graph(dtype, model_dirs, tiny_configs, oracle, cuda_kernels):
+    """Decode-only steps run from a captured graph; the logits are those of the plain path."""
+    from inferflux_b200.engine import ModelRunner
+    from inferflux_b200.models import load_model
+    name = "B"
+    cfg, page = tiny_configs[name]
+    d, _ = model_dirs[name]
+    reqs = {k: v for k, v in list(requests_for(cfg).items())[:3]}
+    steps = helpers.trace_tail(reqs, tail=20)
+    _c, model = load_model(d, dtype=dtype, device="cuda:0")
+    runner = ModelRunner(model, cuda_kernels, page_size=page, num_pages=MAX_TOKENS // page, max_seqs=8,
+                         cuda_graphs=True)
+    got = helpers.collect(steps, helpers.run_steps_in_process(runner, steps), cfg.vocab_size)
+    assert runner.graph_replays >= 30
+    check(got, {k: oracle[name][dtype][k] for k in reqs}, dtype, f"graph replay {dtype}")
