@@ -1,0 +1,108 @@
+"""Generation through the Python entry point on the GPU: greedy tokens against the
+plain implementation, long decoding, the first tokens of a sequence, sampling, and
+what the engine does without its extension."""
+import numpy as np
+import pytest
+import torch
+
+import helpers
+from plain import plain_qwen2
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_greedy_generation_matches_the_plain_implementation(name, model_dirs, tiny_configs):
+    from inferflux_b200 import Engine, SamplingParams
+    cfg, page = tiny_configs[name]
+    d, _ = model_dirs[name]
+    raw, W = plain_qwen2.load_model_dir(d)
+    prompts = [helpers.random_tokens(cfg.vocab_size, n, 300 + i) for i, n in enumerate([7, 19, 33, 1])]
+    want = [plain_qwen2.greedy_generate(raw, W, p, 16) for p in prompts]
+    eng = Engine(d, dtype="float32", kv_page_size=page, kv_num_pages=64, kv_max_batch=4, chunked_prefill_tokens=16,
+                 max_batch_tokens=40)
+    res = eng.generate(prompts, SamplingParams(temperature=0.0), max_tokens=16)
+    assert [r.token_ids for r in res] == want
+    assert all(r.finish_reason == "length" and r.prompt_tokens == len(p) for r, p in zip(res, prompts))
+    assert eng.runner.graph_replays > 0 and eng.kernels.launches > 0
+    # few pages: requests are preempted and recomputed, the tokens stay the same
+    small = Engine(d, dtype="float32", kv_page_size=page, kv_num_pages=-(-70 // page), kv_max_batch=4,
+                   chunked_prefill_tokens=16, max_batch_tokens=40)
+    res = small.generate(prompts, SamplingParams(temperature=0.0), max_tokens=16)
+    assert [r.token_ids for r in res] == want and small.stats.preemptions > 0
+
+
+def test_bfloat16_generation_follows_the_logits(model_dirs, tiny_configs):
+    """In bfloat16 a near-tie may go the other way, so compare step by step: every
+    token the engine picks must be (nearly) the best under the plain logits of the
+    engine's own sequence so far."""
+    from inferflux_b200 import Engine, SamplingParams
+    cfg, page = tiny_configs["B"]
+    d, _ = model_dirs["B"]
+    raw, W = plain_qwen2.load_model_dir(d)
+    W = {k: v.to(torch.bfloat16) for k, v in W.items()}
+    prompt = helpers.random_tokens(cfg.vocab_size, 25, 77)
+    eng = Engine(d, dtype="bfloat16", kv_page_size=page, kv_num_pages=32, kv_max_batch=2)
+    out = eng.generate([prompt], SamplingParams(temperature=0.0), max_tokens=24)[0].token_ids
+    logits = plain_qwen2.forward(raw, W, prompt + out, dtype=torch.float64)
+    scale = float(logits.abs().max())
+    for i, tok in enumerate(out):
+        row = logits[len(prompt) - 1 + i]
+        assert float(row.max() - row[tok]) < 0.04 * scale, f"token {i} is not among the best of its position"
+
+
+@pytest.mark.parametrize("dtype,tol", [("float32", 1e-4), ("bfloat16", None)])
+def test_long_decoding_and_first_tokens(dtype, tol, model_dirs, tiny_configs, cuda_kernels):
+    """One request decoded token by token for hundreds of steps, across many pages and
+    past the window; the very first positions (one key, two keys) are checked too."""
+    from inferflux_b200.engine import ModelRunner, StepEntry
+    from inferflux_b200.models import load_model
+    cfg, page = tiny_configs["C"]
+    d, _ = model_dirs["C"]
+    toks = helpers.random_tokens(cfg.vocab_size, 330, 55)
+    want = helpers.plain_logits(d, {"r": toks}, weights_as=torch.bfloat16 if dtype == "bfloat16" else None)["r"]
+    _c, model = load_model(d, dtype=dtype, device="cuda:0")
+    runner = ModelRunner(model, cuda_kernels, page_size=page, num_pages=24, max_seqs=2, cuda_graphs=True)
+    rows = [runner.step([StepEntry("r", [t], [0])])[0].cpu().numpy() for t in toks]
+    got = np.stack(rows)
+    bound = tol if tol else 0.03 * float(np.abs(want).max())
+    d_ = np.abs(got - want).max(axis=1)
+    assert float(d_.max()) < bound, f"first wrong position {int(np.argmax(d_ > bound))}, diff {float(d_.max())}"
+    assert runner.graph_replays > 300
+
+
+def test_sampling_through_the_entry_point(model_dirs, tiny_configs):
+    from inferflux_b200 import Engine, SamplingParams
+    cfg, page = tiny_configs["B"]
+    d, _ = model_dirs["B"]
+    prompts = [helpers.random_tokens(cfg.vocab_size, n, 400 + i) for i, n in enumerate([1, 4, 50, 97, 130])]
+    sp = [SamplingParams(temperature=0.8, seed=7 + i) for i in range(5)]
+
+    def run(subset, **kw):
+        eng = Engine(d, dtype="float32", kv_page_size=page, kv_num_pages=64, kv_max_batch=8, **kw)
+        return [r.token_ids for r in eng.generate([prompts[i] for i in subset], [sp[i] for i in subset], max_tokens=12)]
+    a = run(range(5), chunked_prefill_tokens=32, max_batch_tokens=64)
+    assert a == run(range(5), chunked_prefill_tokens=32, max_batch_tokens=64), "a fixed seed did not repeat"
+    assert [a[3]] == run([3], chunked_prefill_tokens=512), "a request's draw depends on its batch"
+    # penalties, top-k = 1 and logit bias go through the same path
+    eng = Engine(d, dtype="float32", kv_page_size=page, kv_num_pages=64, kv_max_batch=8)
+    greedy = eng.generate([prompts[2]], SamplingParams(temperature=0.0), max_tokens=8)[0].token_ids
+    topk1 = eng.generate([prompts[2]], SamplingParams(temperature=0.9, top_k=1, seed=3), max_tokens=8)[0].token_ids
+    assert topk1 == greedy
+    forced = eng.generate([prompts[2]], SamplingParams(temperature=0.0, logit_bias={5: 1000.0}), max_tokens=4)[0]
+    assert forced.token_ids == [5, 5, 5, 5]
+    pen = eng.generate([prompts[2]], SamplingParams(temperature=0.0, logit_bias={5: 1000.0}, presence_penalty=2000.0),
+                       max_tokens=3)[0].token_ids
+    assert pen[0] == 5 and pen[1] != 5
+    stop = eng.generate([prompts[2]], SamplingParams(temperature=0.0), max_tokens=8, eos_token_id=greedy[2])[0]
+    assert stop.finish_reason == "stop" and stop.token_ids == greedy[:3]
+
+
+def test_no_extension_no_engine(monkeypatch, model_dirs):
+    """If the kernel library cannot be had the engine refuses to start."""
+    from inferflux_b200.csrc import BuildError, build, ops
+    import inferflux_b200.csrc.build as b
+    monkeypatch.setattr(ops, "load_library", lambda: (_ for _ in ()).throw(BuildError("nvcc not found")))
+    from inferflux_b200 import Engine
+    with pytest.raises(BuildError):
+        Engine(model_dirs["A"][0], dtype="float32")
