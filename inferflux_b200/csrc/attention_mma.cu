@@ -16,16 +16,23 @@
 // split of the key range.  The query heads that share the key/value head (up to
 // 16) are the 16 rows of the MMA tile, so every key and value is read once for all
 // of them.  Each warp walks its own 16-key tiles through a 3-stage cp.async
-// pipeline; the warps' partial results are merged in shared memory, and when the
-// key range is split over several blocks each writes (maximum, sum, unnormalised
-// output) to a scratch buffer that a second kernel merges.
+// pipeline; the warps' partial results are merged in shared memory.  When the key
+// range is split, the blocks of one (token, key/value head) form a thread-block
+// cluster (up to 8): after a cluster barrier each block merges its share of the
+// head dimensions from all blocks' shared memory (distributed shared memory), in
+// block order - no scratch in global memory, no second kernel, nothing spins.
+// Both kernels copy the block-table entries of their key range to shared memory
+// first, so that page lookups do not sit on the critical path of the loads.
 //
 // Head sizes: 16, 32, 48, 64, 80, 96, 112, 128 and 256.  Others, and query groups
 // larger than 16 in decoding, are refused (the caller then uses the generic kernel).
+#include <cooperative_groups.h>
+
 #include "common.cuh"
 
 namespace ifx {
 
+namespace cg = cooperative_groups;
 typedef __nv_bfloat16 bf16;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -61,7 +68,8 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 }
 
 struct PageMap {
-  const int* table;      // this request's row of the block table
+  const int* table;      // this request's row of the block table, or a shared-memory copy of a part of it
+  int blk_base;          // the logical block that table[0] stands for
   int page_size, page_shift, num_pages, nkv, g;
   // Element offset of key `k`'s row (head g) in the pool; the value row lies v_off further.
   __device__ __forceinline__ size_t key_row(int k, int d) const {
@@ -73,7 +81,7 @@ struct PageMap {
       blk = k / page_size;
       off = k - blk * page_size;
     }
-    int page = table[blk];
+    int page = table[blk - blk_base];
     if (page < 0 || page >= num_pages) page = 0;          // a broken table must not leave the pool
     return ((((size_t)page * 2) * nkv + g) * page_size + off) * d;
   }
@@ -85,24 +93,35 @@ __global__ void __launch_bounds__(128)
 attn_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kv_pool, const int* __restrict__ block_table,
                     const int* __restrict__ tiles, const int* __restrict__ req_slot, bf16* __restrict__ out, int nq,
                     int nkv, int page_size, int page_shift, int max_blocks, int num_pages, int window,
-                    float scale_log2) {
+                    float scale_log2, int tbl_cap) {
   constexpr int LDS = D + 8;            // shared-memory row stride in elements
   constexpr int CPR = D / 8;            // 16-byte chunks per row
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* q_s = reinterpret_cast<bf16*>(smem_raw);        // [64][LDS]
   bf16* k_s = q_s + 64 * LDS;                           // [2][64][LDS]
   bf16* v_s = k_s + 2 * 64 * LDS;                       // [2][64][LDS]
+  int* tbl_s = reinterpret_cast<int*>(v_s + 2 * 64 * LDS);   // [tbl_cap] block-table entries of this tile's keys
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int* tile = tiles + (size_t)blockIdx.x * 4;
   const int r = tile[0], row0 = tile[1], rows = tile[2], pos0 = tile[3];
   const int h = blockIdx.y;
-  PageMap pm{block_table + (size_t)req_slot[r] * max_blocks, page_size, page_shift, num_pages, nkv, h / (nq / nkv)};
+  const int* table_g = block_table + (size_t)req_slot[r] * max_blocks;
+  PageMap pm{table_g, 0, page_size, page_shift, num_pages, nkv, h / (nq / nkv)};
   const size_t v_off = (size_t)nkv * page_size * D;
 
   const int kfirst = window > 0 ? max(0, pos0 - window + 1) : 0;
   const int kend = pos0 + rows;
   const int tile_begin = kfirst >> 6, tile_end = (kend + 63) >> 6;
+  {   // the block-table entries of keys [kfirst, kend) go to shared memory once
+    const int b0 = kfirst / page_size, b1 = (kend - 1) / page_size;
+    if (b1 - b0 + 1 <= tbl_cap) {
+      for (int i = tid; i <= b1 - b0; i += 128) tbl_s[i] = table_g[b0 + i];
+      pm.table = tbl_s;
+      pm.blk_base = b0;
+      __syncthreads();
+    }
+  }
 
   for (int i = tid; i < 64 * CPR; i += 128) {
     const int row = i / CPR, c = i % CPR;
@@ -244,23 +263,32 @@ attn_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kv_pool
 template <int D, int STAGES>
 __global__ void __launch_bounds__(128)
 attn_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kv_pool, const int* __restrict__ block_table,
-                   const int* __restrict__ decode_rows, const int* __restrict__ positions,
-                   const int* __restrict__ token_req, const int* __restrict__ req_slot, float* __restrict__ part_o,
-                   float* __restrict__ part_ml, bf16* __restrict__ out, int nq, int nkv, int page_size, int page_shift,
-                   int max_blocks, int num_pages, int window, float scale_log2, int num_splits) {
+                   const int4* __restrict__ decode_meta, bf16* __restrict__ out, int nq, int nkv, int page_size,
+                   int page_shift, int max_blocks, int num_pages, int window, float scale_log2, int tbl_cap) {
   constexpr int LDS = D + 8;
   constexpr int CPR = D / 8;
   constexpr int STAGE_ELEMS = 2 * 16 * LDS;             // K tile then V tile
+  constexpr int STAGE_BYTES_ALL = 4 * STAGES * STAGE_ELEMS * 2;
+  constexpr int MERGE_BYTES = (4 * 16 * D + 2 * 4 * 16) * 4;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* q_s = reinterpret_cast<bf16*>(smem_raw);        // [16][LDS]
   bf16* stage_base = q_s + 16 * LDS;                    // [4 warps][STAGES][2][16][LDS]
+  constexpr int FIN_BYTES = (16 * D + 32) * 4;
+  constexpr int WORK_BYTES = STAGE_BYTES_ALL > MERGE_BYTES + FIN_BYTES ? STAGE_BYTES_ALL : MERGE_BYTES + FIN_BYTES;
+  // the block's merged result lives behind the warps' merge buffers, inside the (by then free) staging area
+  float* fin_o = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(stage_base) + MERGE_BYTES);   // [16][D]
+  float* fin_m = fin_o + 16 * D;                        // [16] this block's maximum per row (log2 domain)
+  float* fin_l = fin_m + 16;                            // [16] this block's sum per row
+  int* tbl_s = reinterpret_cast<int*>(reinterpret_cast<unsigned char*>(stage_base) + WORK_BYTES);   // [tbl_cap]
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int item = blockIdx.x, g = blockIdx.y, split = blockIdx.z;
+  const int item = blockIdx.x, g = blockIdx.y, split = blockIdx.z, num_splits = gridDim.z;
   const int G = nq / nkv;
-  const int t = decode_rows[item];
-  const int pos = positions[t];
-  PageMap pm{block_table + (size_t)req_slot[token_req[t]] * max_blocks, page_size, page_shift, num_pages, nkv, g};
+  const int4 meta = decode_meta[item];                  // (flat token row, position, request slot, -)
+  const int t = meta.x;
+  const int pos = meta.y;
+  const int* table_g = block_table + (size_t)meta.z * max_blocks;
+  PageMap pm{table_g, 0, page_size, page_shift, num_pages, nkv, g};
   const size_t v_off = (size_t)nkv * page_size * D;
 
   const int kfirst = window > 0 ? max(0, pos - window + 1) : 0;
@@ -268,6 +296,14 @@ attn_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kv_pool,
   const int per_split = (((kend - kfirst + num_splits - 1) / num_splits) + 63) / 64 * 64;
   const int k0 = kfirst + split * per_split;
   const int k1 = min(kend, k0 + per_split);
+  if (k0 < k1) {   // the block-table entries of keys [k0, k1) go to shared memory once
+    const int b0 = k0 / page_size, b1 = (k1 - 1) / page_size;
+    if (b1 - b0 + 1 <= tbl_cap) {
+      for (int i = tid; i <= b1 - b0; i += 128) tbl_s[i] = table_g[b0 + i];
+      pm.table = tbl_s;
+      pm.blk_base = b0;
+    }
+  }
 
   for (int i = tid; i < 16 * CPR; i += 128) {
     const int row = i / CPR, c = i % CPR;
@@ -432,84 +468,106 @@ attn_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kv_pool,
     if (num_splits == 1) {
       out[((size_t)t * nq + head) * D + dim] = __float2bfloat16_rn(L > 0.0f ? O / L : 0.0f);
     } else {
-      const size_t p = ((size_t)item * nq + head) * num_splits + split;
-      part_o[p * D + dim] = O;
+      fin_o[row * D + dim] = O;
       if (dim == 0) {
-        part_ml[p * 2] = M;
-        part_ml[p * 2 + 1] = L;
+        fin_m[row] = M;
+        fin_l[row] = L;
       }
     }
   }
-}
-
-// Merge of the splits: out = sum_s 2^(m_s - M) O_s / sum_s 2^(m_s - M) l_s.
-__global__ void attn_decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                         const int* __restrict__ decode_rows, bf16* __restrict__ out, int nq, int d,
-                                         int num_splits) {
-  const int item = blockIdx.x, head = blockIdx.y;
-  const size_t p0 = ((size_t)item * nq + head) * num_splits;
-  float M = -INFINITY;
-  for (int s = 0; s < num_splits; ++s) M = fmaxf(M, part_ml[(p0 + s) * 2]);
-  const int t = decode_rows[item];
-  for (int dim = threadIdx.x; dim < d; dim += blockDim.x) {
+  if (num_splits == 1) return;
+  // ---- merge over the cluster: block `split` takes dims [split * D / n, (split + 1) * D / n) of every
+  //      head and reads all blocks' (maximum, sum, output) through distributed shared memory, in block order
+  cg::cluster_group cluster = cg::this_cluster();
+  cluster.sync();
+  const int DS = D / num_splits;
+  for (int idx = tid; idx < G * DS; idx += 128) {
+    const int row = idx / DS, dim = split * DS + idx % DS;
+    float ms[8], ls[8], os[8];
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+      if (c < num_splits) {
+        ms[c] = cluster.map_shared_rank(fin_m, c)[row];
+        ls[c] = cluster.map_shared_rank(fin_l, c)[row];
+        os[c] = cluster.map_shared_rank(fin_o, c)[row * D + dim];
+      } else {
+        ms[c] = -INFINITY;
+        ls[c] = os[c] = 0.0f;
+      }
+    }
+    float M = -INFINITY;
+#pragma unroll
+    for (int c = 0; c < 8; ++c) M = fmaxf(M, ms[c]);
     float O = 0.0f, L = 0.0f;
     if (M != -INFINITY) {
-      for (int s = 0; s < num_splits; ++s) {
-        const float f = exp2f(part_ml[(p0 + s) * 2] - M);
-        O += f * part_o[(p0 + s) * d + dim];
-        L += f * part_ml[(p0 + s) * 2 + 1];
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        const float f = exp2f(ms[c] - M);
+        O += f * os[c];
+        L += f * ls[c];
       }
     }
-    out[((size_t)t * nq + head) * d + dim] = __float2bfloat16_rn(L > 0.0f ? O / L : 0.0f);
+    out[((size_t)t * nq + g * G + row) * D + dim] = __float2bfloat16_rn(L > 0.0f ? O / L : 0.0f);
   }
+  cluster.sync();                                       // nobody leaves while its shared memory is being read
 }
 
 template <int D>
 int launch_prefill(const bf16* q, const bf16* kv_pool, const int* block_table, const int* tiles, const int* req_slot,
                    bf16* out, int num_tiles, int nq, int nkv, int page_size, int page_shift, int max_blocks,
-                   int num_pages, int window, float scale_log2, cudaStream_t stream) {
-  constexpr int smem = (64 + 4 * 64) * (D + 8) * 2;
-  static bool configured = false;
-  if (!configured) {
+                   int num_pages, int window, float scale_log2, int max_keys, cudaStream_t stream) {
+  constexpr int tile_bytes = (64 + 4 * 64) * (D + 8) * 2;
+  int tbl_cap = max_keys / page_size + 2;               // entries a tile can need
+  if (tbl_cap > 8192) tbl_cap = 0;                      // too long to copy: look pages up in global memory
+  const int smem = tile_bytes + tbl_cap * 4;
+  static int configured = 0;
+  if (smem > configured) {
     cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return (int)e;
-    configured = true;
+    configured = smem;
   }
   dim3 grid(num_tiles, nq);
   attn_prefill_kernel<D><<<grid, 128, smem, stream>>>(q, kv_pool, block_table, tiles, req_slot, out, nq, nkv, page_size,
-                                                      page_shift, max_blocks, num_pages, window, scale_log2);
+                                                      page_shift, max_blocks, num_pages, window, scale_log2, tbl_cap);
   IFX_CHECK_LAUNCH();
   return 0;
 }
 
 template <int D>
-int launch_decode(const bf16* q, const bf16* kv_pool, const int* block_table, const int* decode_rows,
-                  const int* positions, const int* token_req, const int* req_slot, float* part_o, float* part_ml,
-                  bf16* out, int num_items, int nq, int nkv, int page_size, int page_shift, int max_blocks,
-                  int num_pages, int window, float scale_log2, int num_splits, cudaStream_t stream) {
+int launch_decode(const bf16* q, const bf16* kv_pool, const int* block_table, const int4* decode_meta, bf16* out,
+                  int num_items, int nq, int nkv, int page_size, int page_shift, int max_blocks, int num_pages,
+                  int window, float scale_log2, int num_splits, int max_keys, cudaStream_t stream) {
   constexpr int STAGES = D <= 128 ? 3 : 2;
   constexpr int stage_bytes = 4 * STAGES * 2 * 16 * (D + 8) * 2;
   constexpr int merge_bytes = (4 * 16 * D + 2 * 4 * 16) * 4;
-  constexpr int smem = 16 * (D + 8) * 2 + (stage_bytes > merge_bytes ? stage_bytes : merge_bytes);
-  static bool configured = false;
-  if (!configured) {
+  const int per_split = (((max_keys + num_splits - 1) / num_splits) + 63) / 64 * 64;
+  int tbl_cap = per_split / page_size + 2;              // entries a split can need
+  if (tbl_cap > 8192) tbl_cap = 0;
+  constexpr int fin_bytes = (16 * D + 32) * 4;
+  constexpr int work_bytes = stage_bytes > merge_bytes + fin_bytes ? stage_bytes : merge_bytes + fin_bytes;
+  const int smem = 16 * (D + 8) * 2 + work_bytes + tbl_cap * 4;
+  static int configured = 0;
+  if (smem > configured) {
     cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<D, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          smem);
     if (e != cudaSuccess) return (int)e;
-    configured = true;
+    configured = smem;
   }
-  dim3 grid(num_items, nkv, num_splits);
-  attn_decode_kernel<D, STAGES><<<grid, 128, smem, stream>>>(q, kv_pool, block_table, decode_rows, positions, token_req,
-                                                             req_slot, part_o, part_ml, out, nq, nkv, page_size,
-                                                             page_shift, max_blocks, num_pages, window, scale_log2,
-                                                             num_splits);
-  IFX_CHECK_LAUNCH();
-  if (num_splits > 1) {
-    dim3 mgrid(num_items, nq);
-    attn_decode_merge_kernel<<<mgrid, D >= 128 ? 128 : 64, 0, stream>>>(part_o, part_ml, decode_rows, out, nq, D,
-                                                                        num_splits);
-    IFX_CHECK_LAUNCH();
-  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(num_items, nkv, num_splits);
+  cfg.blockDim = dim3(128);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 1;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = num_splits;
+  cfg.attrs = attr;
+  cfg.numAttrs = num_splits > 1 ? 1 : 0;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, attn_decode_kernel<D, STAGES>, q, kv_pool, block_table, decode_meta, out, nq,
+                                     nkv, page_size, page_shift, max_blocks, num_pages, window, scale_log2, tbl_cap);
+  if (e != cudaSuccess) return (int)e;
   return 0;
 }
 
@@ -546,38 +604,41 @@ int ifx_attention_mma_supports(int d) {
 }
 
 // tiles: int32 [num_tiles, 4] = (request index, first flat row, rows <= 64, first position).
+// max_keys: no request of the step holds more keys than this (sizes the shared-memory copy of the block table).
 int ifx_attention_prefill_bf16(const void* q, const void* kv_pool, const int* block_table, const int* tiles,
                                const int* req_slot, void* out, int num_tiles, int nq, int nkv, int d, int page_size,
-                               int max_blocks, int num_pages, int window, float scale, cudaStream_t stream) {
+                               int max_blocks, int num_pages, int window, float scale, int max_keys,
+                               cudaStream_t stream) {
   if (num_tiles <= 0) return 0;
   if (nq <= 0 || nkv <= 0 || nq % nkv || page_size <= 0 || max_blocks <= 0 || nq > 65535) return IFX_E_BADARG;
   const float scale_log2 = scale * 1.4426950408889634f;
   const int ps = shift_of(page_size);
 #define CALL(DD)                                                                                                   \
   launch_prefill<DD>((const bf16*)q, (const bf16*)kv_pool, block_table, tiles, req_slot, (bf16*)out, num_tiles, nq, \
-                     nkv, page_size, ps, max_blocks, num_pages, window, scale_log2, stream)
+                     nkv, page_size, ps, max_blocks, num_pages, window, scale_log2, max_keys, stream)
   IFX_DISPATCH_D(d, CALL)
 #undef CALL
 }
 
-// part_o: float32 [num_items, nq, num_splits, d]; part_ml: float32 [num_items, nq, num_splits, 2]
-// (both unused when num_splits == 1).
-int ifx_attention_decode_bf16(const void* q, const void* kv_pool, const int* block_table, const int* decode_rows,
-                              const int* positions, const int* token_req, const int* req_slot, float* part_o,
-                              float* part_ml, void* out, int num_items, int nq, int nkv, int d, int page_size,
-                              int max_blocks, int num_pages, int window, float scale, int num_splits,
+// decode_meta: int32 [num_items, 4] = (flat token row, position, request slot, unused).
+// num_splits: 1, 2, 4 or 8 blocks (one cluster) share a token's key range; it must divide d.
+// max_keys: no token of the step sees more keys than this.
+int ifx_attention_decode_bf16(const void* q, const void* kv_pool, const int* block_table, const int* decode_meta,
+                              void* out, int num_items, int nq, int nkv, int d, int page_size, int max_blocks,
+                              int num_pages, int window, float scale, int num_splits, int max_keys,
                               cudaStream_t stream) {
   if (num_items <= 0) return 0;
-  if (nq <= 0 || nkv <= 0 || nq % nkv || nq / nkv > 16 || page_size <= 0 || max_blocks <= 0 || num_splits <= 0 ||
-      nkv > 65535 || num_splits > 65535 || nq > 65535)
+  if (nq <= 0 || nkv <= 0 || nq % nkv || nq / nkv > 16 || page_size <= 0 || max_blocks <= 0 || nkv > 65535 ||
+      nq > 65535)
     return IFX_E_BADARG;
-  if (num_splits > 1 && (part_o == nullptr || part_ml == nullptr)) return IFX_E_BADARG;
+  if (!(num_splits == 1 || num_splits == 2 || num_splits == 4 || num_splits == 8) || d % num_splits)
+    return IFX_E_BADARG;
   const float scale_log2 = scale * 1.4426950408889634f;
   const int ps = shift_of(page_size);
-#define CALL(DD)                                                                                                     \
-  launch_decode<DD>((const bf16*)q, (const bf16*)kv_pool, block_table, decode_rows, positions, token_req, req_slot,  \
-                    part_o, part_ml, (bf16*)out, num_items, nq, nkv, page_size, ps, max_blocks, num_pages, window,   \
-                    scale_log2, num_splits, stream)
+#define CALL(DD)                                                                                                  \
+  launch_decode<DD>((const bf16*)q, (const bf16*)kv_pool, block_table, (const int4*)decode_meta, (bf16*)out,     \
+                    num_items, nq, nkv, page_size, ps, max_blocks, num_pages, window, scale_log2, num_splits,     \
+                    max_keys, stream)
   IFX_DISPATCH_D(d, CALL)
 #undef CALL
 }

@@ -24,20 +24,29 @@ __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict_
 }
 
 // -------------------------------------------------------------------- RMSNorm
-// y = x * rsqrt(mean(x^2) + eps) * w.  With ADD, x += delta first (x is updated in
-// place) and the norm is taken of the sum.  One block per row.
-template <typename T, bool ADD>
-__global__ void rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ delta,
-                               const float* __restrict__ w, T* __restrict__ out, int hidden, float eps) {
+// y = x * rsqrt(mean(x^2) + eps) * w.  ADD = 1: x += delta first (x is updated in
+// place) and the norm is taken of the sum.  ADD = 2: the delta arrives as float32
+// partial sums [splits, rows, hidden] of a K-split matrix product; they are added
+// in split order, so the result does not depend on timing.  One block per row.
+template <typename T, int ADD>
+__global__ void rmsnorm_kernel(float* __restrict__ x, const void* __restrict__ delta_raw,
+                               const float* __restrict__ w, T* __restrict__ out, int hidden, float eps,
+                               int num_splits, size_t split_stride) {
   __shared__ float scratch[32];
   const size_t row = blockIdx.x;
   float* xr = x + row * hidden;
-  const T* dr = ADD ? delta + row * hidden : nullptr;
+  const T* dr = ADD == 1 ? reinterpret_cast<const T*>(delta_raw) + row * hidden : nullptr;
+  const float* pr = ADD == 2 ? reinterpret_cast<const float*>(delta_raw) + row * hidden : nullptr;
   float ss = 0.0f;
   for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
     float v = xr[i];
-    if (ADD) {
+    if (ADD == 1) {
       v += to_f32(dr[i]);
+      xr[i] = v;
+    } else if (ADD == 2) {
+      float d = 0.0f;
+      for (int s = 0; s < num_splits; ++s) d += pr[(size_t)s * split_stride + i];
+      v += d;
       xr[i] = v;
     }
     ss += v * v;
@@ -46,6 +55,99 @@ __global__ void rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ delt
   const float r = rsqrtf(ss / (float)hidden + eps);
   T* o = out + row * hidden;
   for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = from_f32<T>(xr[i] * r * w[i]);
+}
+
+// x += sum of K-split partial sums, then RMSNorm, spread over many blocks: block
+// (row, chunk) adds the slices of its 512 columns in split order, updates x and
+// leaves its sum of squares in `sumsq[row, chunk]`; the block that finishes a row
+// last (a ticket counter per row, reset for the next launch) adds the chunk sums in
+// chunk order and writes the normalised row.  Nothing waits on another block.
+// Loads are issued in batches before anything depends on them: with a handful of
+// rows the kernel's time is a few round trips to L2, not bandwidth.
+constexpr int kNormChunk = 512;
+constexpr int kNormBatch = 8;
+
+template <typename T>
+__global__ void __launch_bounds__(128)
+reduce_add_rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ part, const float* __restrict__ w,
+                          T* __restrict__ out, int hidden, float eps, int num_splits, size_t split_stride,
+                          float* __restrict__ sumsq, int* __restrict__ tickets, int chunks) {
+  __shared__ float scratch[32];
+  __shared__ int is_last;
+  const int row = blockIdx.x, chunk = blockIdx.y;
+  float* xr = x + (size_t)row * hidden;
+  const float* pr = part + (size_t)row * hidden;
+  const int c0 = chunk * kNormChunk + threadIdx.x * 4;
+  float ss = 0.0f;
+  if (c0 + 3 < hidden && (hidden & 3) == 0) {
+    float4 v = *reinterpret_cast<float4*>(xr + c0);
+    float4 d = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int s0 = 0; s0 < num_splits; s0 += kNormBatch) {
+      float4 p[kNormBatch];
+#pragma unroll
+      for (int j = 0; j < kNormBatch; ++j)
+        p[j] = s0 + j < num_splits ? __ldcg(reinterpret_cast<const float4*>(pr + (size_t)(s0 + j) * split_stride + c0))
+                                   : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int j = 0; j < kNormBatch; ++j) {
+        d.x += p[j].x; d.y += p[j].y; d.z += p[j].z; d.w += p[j].w;
+      }
+    }
+    v.x += d.x; v.y += d.y; v.z += d.z; v.w += d.w;
+    *reinterpret_cast<float4*>(xr + c0) = v;
+    ss = v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+  } else {
+    for (int c = c0; c < min(c0 + 4, hidden); ++c) {
+      float d = 0.0f;
+      for (int s = 0; s < num_splits; ++s) d += pr[(size_t)s * split_stride + c];
+      const float v = xr[c] + d;
+      xr[c] = v;
+      ss += v * v;
+    }
+  }
+  __threadfence();                       // this thread's part of x is out before the ticket is taken
+  ss = block_sum(ss, scratch);
+  if (threadIdx.x == 0) {
+    sumsq[(size_t)row * chunks + chunk] = ss;
+    __threadfence();
+    const int t = atomicAdd(&tickets[row], 1);
+    is_last = (t == chunks - 1);
+    if (is_last) tickets[row] = 0;
+  }
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  float total = 0.0f;
+  for (int c = 0; c < chunks; ++c) total += __ldcg(&sumsq[(size_t)row * chunks + c]);
+  const float r = rsqrtf(total / (float)hidden + eps);
+  T* o = out + (size_t)row * hidden;
+  if ((hidden & 3) == 0) {
+    const int n4 = hidden >> 2;
+    for (int i0 = threadIdx.x; i0 < n4; i0 += 128 * kNormBatch) {
+      float4 xv[kNormBatch], wv[kNormBatch];
+#pragma unroll
+      for (int j = 0; j < kNormBatch; ++j) {
+        const int i = i0 + j * 128;
+        if (i < n4) {
+          xv[j] = __ldcg(reinterpret_cast<const float4*>(xr) + i);
+          wv[j] = *(reinterpret_cast<const float4*>(w) + i);
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < kNormBatch; ++j) {
+        const int i = i0 + j * 128;
+        if (i < n4) {
+          T* dst = o + (size_t)i * 4;
+          dst[0] = from_f32<T>(xv[j].x * r * wv[j].x);
+          dst[1] = from_f32<T>(xv[j].y * r * wv[j].y);
+          dst[2] = from_f32<T>(xv[j].z * r * wv[j].z);
+          dst[3] = from_f32<T>(xv[j].w * r * wv[j].w);
+        }
+      }
+    }
+  } else {
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = from_f32<T>(__ldcg(&xr[i]) * r * w[i]);
+  }
 }
 
 // ------------------------------------------------------------------- SiLU*up
@@ -92,6 +194,28 @@ __global__ void residual_add_kernel(float* __restrict__ x, const T* __restrict__
   if (idx < total) x[idx] += to_f32(delta[idx]);
 }
 
+// x += sum over splits of float32 partial sums [splits, rows*hidden], in split order.
+__global__ void residual_add_partial_kernel(float* __restrict__ x, const float* __restrict__ part, size_t total,
+                                            int num_splits) {
+  size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  float d = 0.0f;
+  for (int s = 0; s < num_splits; ++s) d += part[(size_t)s * total + idx];
+  x[idx] += d;
+}
+
+// out = sum over splits (+ bias[col]) rounded to T: the plain way to consume partial sums.
+template <typename T>
+__global__ void reduce_partial_kernel(const float* __restrict__ part, const float* __restrict__ bias,
+                                      T* __restrict__ out, size_t total, int cols, int num_splits) {
+  size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  float d = 0.0f;
+  for (int s = 0; s < num_splits; ++s) d += part[(size_t)s * total + idx];
+  if (bias) d += bias[idx % cols];
+  out[idx] = from_f32<T>(d);
+}
+
 __global__ void gather_rows_kernel(const float* __restrict__ x, const int* __restrict__ rows,
                                    float* __restrict__ out, int hidden, int num_src_rows) {
   const int r = blockIdx.x;
@@ -135,27 +259,75 @@ int ifx_embed(const void* table, const int* tokens, float* out, int num_tokens, 
   return 0;
 }
 
-// delta == nullptr: plain norm of x.  Otherwise x += delta, then the norm of the sum.
+// delta == nullptr: plain norm of x.  Otherwise x += delta, then the norm of the sum;
+// num_splits > 0 says that delta is float32 partial sums [num_splits, rows, hidden].
 int ifx_rmsnorm(float* x, const void* delta, const float* w, void* out, int rows, int hidden, float eps,
-                int dtype, cudaStream_t stream) {
+                int num_splits, int dtype, cudaStream_t stream) {
   if (rows <= 0) return 0;
-  if (hidden <= 0) return IFX_E_BADARG;
+  if (hidden <= 0 || num_splits < 0) return IFX_E_BADARG;
   const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
+  const size_t stride = (size_t)rows * hidden;
+#define IFX_NORM(T, ADD) \
+  rmsnorm_kernel<T, ADD><<<rows, threads, 0, stream>>>(x, delta, w, (T*)out, hidden, eps, num_splits, stride)
   if (dtype == IFX_DT_F32) {
-    if (delta)
-      rmsnorm_kernel<float, true><<<rows, threads, 0, stream>>>(x, (const float*)delta, w, (float*)out, hidden, eps);
-    else
-      rmsnorm_kernel<float, false><<<rows, threads, 0, stream>>>(x, nullptr, w, (float*)out, hidden, eps);
+    if (!delta) IFX_NORM(float, 0);
+    else if (num_splits > 0) IFX_NORM(float, 2);
+    else IFX_NORM(float, 1);
   } else if (dtype == IFX_DT_BF16) {
-    if (delta)
-      rmsnorm_kernel<__nv_bfloat16, true><<<rows, threads, 0, stream>>>(x, (const __nv_bfloat16*)delta, w,
-                                                                        (__nv_bfloat16*)out, hidden, eps);
-    else
-      rmsnorm_kernel<__nv_bfloat16, false><<<rows, threads, 0, stream>>>(x, nullptr, w, (__nv_bfloat16*)out,
-                                                                         hidden, eps);
+    if (!delta) IFX_NORM(__nv_bfloat16, 0);
+    else if (num_splits > 0) IFX_NORM(__nv_bfloat16, 2);
+    else IFX_NORM(__nv_bfloat16, 1);
   } else {
     return IFX_E_DTYPE;
   }
+#undef IFX_NORM
+  IFX_CHECK_LAUNCH();
+  return 0;
+}
+
+// The same as ifx_rmsnorm with partial sums, over many blocks.  sumsq: float32
+// [rows, ceil(hidden / 512)] scratch; tickets: int32 [rows], zero before the first call
+// (the kernel leaves them zero).
+int ifx_reduce_add_rmsnorm(float* x, const float* part, const float* w, void* out, int rows, int hidden, float eps,
+                           int num_splits, float* sumsq, int* tickets, int dtype, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (hidden <= 0 || num_splits <= 0 || sumsq == nullptr || tickets == nullptr) return IFX_E_BADARG;
+  const int chunks = (hidden + kNormChunk - 1) / kNormChunk;
+  if (chunks > 65535) return IFX_E_TOOBIG;
+  dim3 grid(rows, chunks);
+  const size_t stride = (size_t)rows * hidden;
+  if (dtype == IFX_DT_F32)
+    reduce_add_rmsnorm_kernel<float><<<grid, 128, 0, stream>>>(x, part, w, (float*)out, hidden, eps, num_splits, stride,
+                                                               sumsq, tickets, chunks);
+  else if (dtype == IFX_DT_BF16)
+    reduce_add_rmsnorm_kernel<__nv_bfloat16><<<grid, 128, 0, stream>>>(x, part, w, (__nv_bfloat16*)out, hidden, eps,
+                                                                       num_splits, stride, sumsq, tickets, chunks);
+  else
+    return IFX_E_DTYPE;
+  IFX_CHECK_LAUNCH();
+  return 0;
+}
+
+int ifx_residual_add_partial(float* x, const float* part, int rows, int hidden, int num_splits, cudaStream_t stream) {
+  if (rows <= 0 || num_splits <= 0) return 0;
+  const size_t total = (size_t)rows * hidden;
+  residual_add_partial_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(x, part, total, num_splits);
+  IFX_CHECK_LAUNCH();
+  return 0;
+}
+
+int ifx_reduce_partial(const float* part, const float* bias, void* out, int rows, int cols, int num_splits, int dtype,
+                       cudaStream_t stream) {
+  if (rows <= 0 || num_splits <= 0) return 0;
+  const size_t total = (size_t)rows * cols;
+  const unsigned blocks = (unsigned)((total + 255) / 256);
+  if (dtype == IFX_DT_F32)
+    reduce_partial_kernel<float><<<blocks, 256, 0, stream>>>(part, bias, (float*)out, total, cols, num_splits);
+  else if (dtype == IFX_DT_BF16)
+    reduce_partial_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(part, bias, (__nv_bfloat16*)out, total, cols,
+                                                                     num_splits);
+  else
+    return IFX_E_DTYPE;
   IFX_CHECK_LAUNCH();
   return 0;
 }

@@ -25,6 +25,25 @@ class KernelError(RuntimeError):
     pass
 
 
+class PartialSum:
+    """The result of a matrix product whose K range was split over thread blocks:
+    float32 partial sums [splits, rows, cols] that the consuming kernel adds, in split
+    order, in the same pass in which it does its own work (residual add and norm, bias
+    and rotation).  `CudaKernels.materialize` gives the plain tensor."""
+
+    def __init__(self, parts: torch.Tensor, dtype: torch.dtype):
+        self.parts = parts
+        self.dtype = dtype                       # the dtype the sum stands for
+
+    @property
+    def shape(self):
+        return self.parts.shape[1:]
+
+    @property
+    def splits(self) -> int:
+        return self.parts.shape[0]
+
+
 def _ptr(t: Optional[torch.Tensor]):
     return ctypes.c_void_p(0 if t is None else t.data_ptr())
 
@@ -62,11 +81,20 @@ class CudaKernels:
                    "ifx_scatter_i32", "ifx_rope_append", "ifx_attention_generic", "ifx_gemm_generic",
                    "ifx_gemm_cublas_bf16", "ifx_cublas_init", "ifx_argmax", "ifx_penalties", "ifx_logit_bias",
                    "ifx_sample", "ifx_attention_mma_supports", "ifx_attention_prefill_bf16",
-                   "ifx_attention_decode_bf16"):
+                   "ifx_attention_decode_bf16", "ifx_gemm_skinny", "ifx_residual_add_partial",
+                   "ifx_reduce_partial", "ifx_reduce_add_rmsnorm", "ifx_argmax_chunks"):
             getattr(self.lib, fn).restype = ctypes.c_int
         with torch.cuda.device(self.device):
             _check(self.lib.ifx_cublas_init(), "cublas init")
-        self.launches = 0            # kernels of this library launched so far (library GEMMs included)
+        self.launches = 0            # kernels of this library launched so far
+        self.library_calls = 0       # cuBLAS products called so far
+        # scratch of the many-block reduce + norm: sums of squares per (row, chunk), a ticket per row
+        self._norm_sumsq = torch.zeros(128 * 64, dtype=torch.float32, device=self.device)
+        self._norm_tickets = torch.zeros(128, dtype=torch.int32, device=self.device)
+        self._argmax_val = torch.zeros(256 * 32, dtype=torch.float32, device=self.device)
+        self._argmax_idx = torch.zeros(256 * 32, dtype=torch.int32, device=self.device)
+        self._argmax_tickets = torch.zeros(256, dtype=torch.int32, device=self.device)
+        self.error_flag = torch.zeros(1, dtype=torch.int32, device=self.device)   # set by a kernel whose bounded wait ran out
 
     # ------------------------------------------------------------- elementwise
     def embed(self, table, token_ids, vocab):
@@ -81,25 +109,54 @@ class CudaKernels:
         _need(x.dtype == torch.float32 and w.dtype == torch.float32, "rmsnorm: x and w must be float32")
         T, H = x.shape
         out = torch.empty((T, H), dtype=out_dtype, device=x.device)
-        _check(self.lib.ifx_rmsnorm(_ptr(x), _ptr(None), _ptr(w), _ptr(out), T, H, ctypes.c_float(eps),
+        _check(self.lib.ifx_rmsnorm(_ptr(x), _ptr(None), _ptr(w), _ptr(out), T, H, ctypes.c_float(eps), 0,
                                     _DT[out_dtype], _stream()), "rmsnorm")
         self.launches += 1
         return out
 
     def add_rmsnorm(self, x, delta, w, eps, out_dtype):
+        """x += delta (in place), then the norm of the sum.  `delta` is a tensor in the run's
+        dtype or a PartialSum, whose slices are added in the same pass."""
         _need(x.dtype == torch.float32 and w.dtype == torch.float32, "add_rmsnorm: x and w must be float32")
-        _need(delta.dtype == out_dtype and delta.shape == x.shape, "add_rmsnorm: delta must match x and the dtype")
         T, H = x.shape
         out = torch.empty((T, H), dtype=out_dtype, device=x.device)
-        _check(self.lib.ifx_rmsnorm(_ptr(x), _ptr(delta), _ptr(w), _ptr(out), T, H, ctypes.c_float(eps),
+        if isinstance(delta, PartialSum):
+            _need(tuple(delta.shape) == (T, H), "add_rmsnorm: partial sums do not match x")
+            chunks = -(-H // 512)
+            if T <= self._norm_tickets.numel() and T * chunks <= self._norm_sumsq.numel():
+                _check(self.lib.ifx_reduce_add_rmsnorm(
+                    _ptr(x), _ptr(delta.parts), _ptr(w), _ptr(out), T, H, ctypes.c_float(eps), delta.splits,
+                    _ptr(self._norm_sumsq), _ptr(self._norm_tickets), _DT[out_dtype], _stream()), "reduce_add_rmsnorm")
+                self.launches += 1
+                return out
+            src, splits = delta.parts, delta.splits
+        else:
+            _need(delta.dtype == out_dtype and delta.shape == x.shape, "add_rmsnorm: delta must match x and the dtype")
+            src, splits = delta, 0
+        _check(self.lib.ifx_rmsnorm(_ptr(x), _ptr(src), _ptr(w), _ptr(out), T, H, ctypes.c_float(eps), splits,
                                     _DT[out_dtype], _stream()), "add_rmsnorm")
         self.launches += 1
         return out
 
     def residual_add(self, x, delta):
         T, H = x.shape
-        _check(self.lib.ifx_residual_add(_ptr(x), _ptr(delta), T, H, _DT[delta.dtype], _stream()), "residual_add")
+        if isinstance(delta, PartialSum):
+            _check(self.lib.ifx_residual_add_partial(_ptr(x), _ptr(delta.parts), T, H, delta.splits, _stream()),
+                   "residual_add")
+        else:
+            _check(self.lib.ifx_residual_add(_ptr(x), _ptr(delta), T, H, _DT[delta.dtype], _stream()), "residual_add")
         self.launches += 1
+
+    def materialize(self, value, bias=None):
+        """A plain tensor from what `linear(..., allow_partial=True)` returned."""
+        if not isinstance(value, PartialSum):
+            return value if bias is None else value + bias.to(value.dtype)
+        T, N = value.shape
+        out = torch.empty((T, N), dtype=value.dtype, device=value.parts.device)
+        _check(self.lib.ifx_reduce_partial(_ptr(value.parts), _ptr(bias), _ptr(out), T, N, value.splits,
+                                           _DT[value.dtype], _stream()), "reduce_partial")
+        self.launches += 1
+        return out
 
     def silu_mul(self, gate_up):
         T, two_i = gate_up.shape
@@ -124,29 +181,80 @@ class CudaKernels:
             self.launches += 1
 
     # ------------------------------------------------------------------ linear
-    def linear(self, a, w, bias=None, out_dtype=None):
-        """out[T, N] = a[T, K] . w[N, K]^T (+ bias), float32 accumulation."""
+    SKINNY_MAX_ROWS = 128
+
+    def linear(self, a, w, bias=None, out_dtype=None, allow_partial=False):
+        """out[T, N] = a[T, K] . w[N, K]^T (+ bias), float32 accumulation.  float32 runs use
+        the CUDA-core product.  bfloat16 runs with up to 128 rows use the tcgen05 weight-streaming
+        kernel; with `allow_partial` a narrow product is split over K and comes back as a
+        PartialSum for a consumer that adds the slices itself.  More rows go to cuBLAS."""
         _need(a.dtype == w.dtype, f"linear: activations are {a.dtype}, weights {w.dtype}")
         _need(a.is_contiguous() and w.is_contiguous(), "linear: operands must be contiguous")
         T, K = a.shape
         N = w.shape[0]
         _need(w.shape[1] == K, f"linear: inner sizes differ ({K} vs {w.shape[1]})")
         out_dtype = out_dtype or a.dtype
-        out = torch.empty((T, N), dtype=out_dtype, device=a.device)
         if T == 0:
-            return out
+            return torch.empty((T, N), dtype=out_dtype, device=a.device)
         if a.dtype == torch.float32:
             _need(out_dtype == torch.float32, "linear: a float32 product gives float32")
+            out = torch.empty((T, N), dtype=out_dtype, device=a.device)
             _check(self.lib.ifx_gemm_generic(_ptr(a), _ptr(w), _ptr(bias), _ptr(out), T, N, K, 0, 0, _stream()),
                    "gemm (float32)")
             self.launches += 1
             return out
+        if T <= self.SKINNY_MAX_ROWS and K % 8 == 0 and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0:
+            tiles = -(-N // 128)
+            kblocks = -(-K // 64)
+            splits = max(1, min(296 // tiles, 10, kblocks // 4)) if allow_partial and bias is None else 1
+            if splits > 1:
+                parts = self.linear_skinny(a, w, None, splits=splits, mode=1)
+                return PartialSum(parts, out_dtype)
+            if tiles >= 74 or allow_partial:
+                return self.linear_skinny(a, w, bias, out_dtype=out_dtype, splits=1, mode=0)
+        out = torch.empty((T, N), dtype=out_dtype, device=a.device)
         _check(self.lib.ifx_gemm_cublas_bf16(_ptr(a), _ptr(w), _ptr(out), T, N, K, _DT[out_dtype], _stream()),
                "gemm (bfloat16)")
-        self.launches += 1
+        self.library_calls += 1
         if bias is not None:
             out += bias.to(out.dtype)
         return out
+
+    def linear_swiglu(self, a, w_gate_up):
+        """silu(a . Wg^T) * (a . Wu^T) with Wg and Wu stacked in w_gate_up [2 I, K]: one kernel
+        with both accumulators for few rows, else the product followed by the activation kernel."""
+        T, K = a.shape
+        inter = w_gate_up.shape[0] // 2
+        if (a.dtype == torch.bfloat16 and 0 < T <= self.SKINNY_MAX_ROWS and K % 8 == 0 and a.data_ptr() % 16 == 0
+                and w_gate_up.data_ptr() % 16 == 0):
+            return self.linear_skinny(a, w_gate_up, None, splits=1, mode=2, n_out=inter, up_row_offset=inter)
+        return self.silu_mul(self.linear(a, w_gate_up))
+
+    def check_errors(self):
+        """Raise if a kernel reported that one of its bounded waits ran out (reads the device flag)."""
+        code = int(self.error_flag.item())
+        if code:
+            self.error_flag.zero_()
+            raise KernelError(f"a kernel gave up waiting on a barrier (code {code}); its output is not valid")
+
+    def linear_skinny(self, a, w, bias=None, out_dtype=None, splits=1, mode=0, n_out=None, up_row_offset=0):
+        """The tcgen05 weight-streaming product for up to 128 token rows.
+        mode 0: out[T, N] (+bias); mode 1: float32 partial sums [splits, T, N]; mode 2: silu(gate) * up."""
+        T, K = a.shape
+        N = n_out if n_out is not None else w.shape[0]
+        _need(a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16, "linear_skinny: bfloat16 only")
+        _need(a.is_contiguous() and w.is_contiguous() and w.shape[1] == K, "linear_skinny: bad operands")
+        out_dtype = out_dtype or torch.bfloat16
+        out = partials = None
+        if mode == 1:
+            partials = torch.empty((splits, T, N), dtype=torch.float32, device=a.device)
+        else:
+            out = torch.empty((T, N), dtype=out_dtype, device=a.device)
+        _check(self.lib.ifx_gemm_skinny(_ptr(a), _ptr(w), _ptr(bias), _ptr(out), _ptr(partials), T, N, K, w.shape[0],
+                                        splits, mode, up_row_offset, int(out_dtype == torch.float32),
+                                        _ptr(self.error_flag), _stream()), "gemm_skinny")
+        self.launches += 1
+        return partials if mode == 1 else out
 
     def linear_generic(self, a, w, bias=None, out_dtype=None):
         """The CUDA-core product for any dtype (used by tests and as the refusal-free path)."""
@@ -161,21 +269,29 @@ class CudaKernels:
 
     # --------------------------------------------------------------- attention
     def rope_append(self, qkv, bias, rotary, nq, nkv, d, ctx, cache):
-        T = qkv.shape[0]
-        _need(qkv.shape[1] == (nq + 2 * nkv) * d, "rope_append: qkv width does not fit the head counts")
-        q_out = torch.empty((T, nq * d), dtype=qkv.dtype, device=qkv.device)
+        """`qkv`: the stacked projections [T, (nq + 2 nkv) d] as a tensor or a PartialSum."""
+        partial, splits = None, 0
+        if isinstance(qkv, PartialSum):
+            partial, splits, dtype, device = qkv.parts, qkv.splits, qkv.dtype, qkv.parts.device
+            T, width = qkv.shape
+            qkv = None
+        else:
+            dtype, device = qkv.dtype, qkv.device
+            T, width = qkv.shape
+        _need(width == (nq + 2 * nkv) * d, "rope_append: qkv width does not fit the head counts")
+        q_out = torch.empty((T, nq * d), dtype=dtype, device=device)
         write = bool(cache.writes and cache.kv is not None)
         kv, table = cache.kv, cache.block_table
         if write:
-            _need(kv.dtype == qkv.dtype, f"rope_append: cache is {kv.dtype}, activations {qkv.dtype}")
+            _need(kv.dtype == dtype, f"rope_append: cache is {kv.dtype}, activations {dtype}")
         rot = 0 if rotary is None else int(rotary.rotary_dim)
         _need(rot <= d, "rope_append: rotary_dim exceeds the head size")
         _check(self.lib.ifx_rope_append(
-            _ptr(qkv), _ptr(bias), _ptr(None if rotary is None else rotary.inv_freq), rot,
+            _ptr(qkv), _ptr(partial), splits, _ptr(bias), _ptr(None if rotary is None else rotary.inv_freq), rot,
             int(bool(rotary.interleaved)) if rotary is not None else 0,
             _ptr(ctx.positions), _ptr(ctx.token_req), _ptr(ctx.req_slot), _ptr(table),
             0 if table is None else table.shape[1], cache.page_size, 0 if kv is None else kv.shape[0],
-            _ptr(kv), _ptr(q_out), T, nq, nkv, d, int(write), _DT[qkv.dtype], _stream()), "rope_append")
+            _ptr(kv), _ptr(q_out), T, nq, nkv, d, int(write), _DT[dtype], _stream()), "rope_append")
         self.launches += 1
         return q_out
 
@@ -199,31 +315,32 @@ class CudaKernels:
         if ctx.num_prefill_tiles:
             _check(self.lib.ifx_attention_prefill_bf16(
                 _ptr(q), _ptr(kv), _ptr(table), _ptr(ctx.prefill_tiles), _ptr(ctx.req_slot), _ptr(out),
-                ctx.num_prefill_tiles, nq, nkv, d, *common, _stream()), "attention (prompt portions)")
+                ctx.num_prefill_tiles, nq, nkv, d, *common, int(ctx.max_kv_len), _stream()),
+                "attention (prompt portions)")
             self.launches += 1
         n = ctx.num_decode_rows
         if n:
             if nq // nkv > 16:
                 self._attention_generic(q, kv, table, ctx, ctx.decode_rows, n, out, nq, nkv, d, common)
                 return out
-            splits = self.decode_splits(n, nkv, ctx.max_kv_len if not win else min(win, ctx.max_kv_len))
-            part_o = part_ml = None
-            if splits > 1:
-                part_o = torch.empty((n, nq, splits, d), dtype=torch.float32, device=q.device)
-                part_ml = torch.empty((n, nq, splits, 2), dtype=torch.float32, device=q.device)
+            max_keys = int(ctx.max_kv_len if not win else min(win, ctx.max_kv_len))
+            splits = self.decode_splits(n, nkv, max_keys)
             _check(self.lib.ifx_attention_decode_bf16(
-                _ptr(q), _ptr(kv), _ptr(table), _ptr(ctx.decode_rows), _ptr(ctx.positions), _ptr(ctx.token_req),
-                _ptr(ctx.req_slot), _ptr(part_o), _ptr(part_ml), _ptr(out), n, nq, nkv, d, *common, splits,
-                _stream()), "attention (decoded tokens)")
-            self.launches += 2 if splits > 1 else 1
+                _ptr(q), _ptr(kv), _ptr(table), _ptr(ctx.decode_meta), _ptr(out), n, nq, nkv, d, *common, splits,
+                max_keys, _stream()), "attention (decoded tokens)")
+            self.launches += 1
         return out
 
     @staticmethod
     def decode_splits(num_tokens, nkv, max_keys):
-        """Into how many thread blocks the key range of a decoded token is cut: enough
-        blocks to fill the 148 SMs twice, but at least 128 keys per block."""
+        """Into how many thread blocks (one cluster: 1, 2, 4 or 8) the key range of a decoded
+        token is cut: enough blocks to fill the 148 SMs twice, but at least 128 keys per block."""
         want = -(-296 // max(1, num_tokens * nkv))
-        return max(1, min(want, max(1, max_keys // 128), 64))
+        limit = max(1, min(want, max_keys // 128, 8))
+        splits = 1
+        while splits * 2 <= limit:
+            splits *= 2
+        return splits
 
     def _attention_generic(self, q, kv, table, ctx, rows, count, out, nq, nkv, d, common):
         _check(self.lib.ifx_attention_generic(
@@ -235,6 +352,11 @@ class CudaKernels:
     def argmax(self, logits):
         R, V = logits.shape
         out = torch.empty((R,), dtype=torch.int32, device=logits.device)
+        if V >= 16384 and R <= 256:                      # long rows, few of them: many blocks per row
+            _check(self.lib.ifx_argmax_chunks(_ptr(logits), _ptr(out), R, V, 32, _ptr(self._argmax_val),
+                                              _ptr(self._argmax_idx), _ptr(self._argmax_tickets), _stream()), "argmax")
+            self.launches += 1
+            return out
         _check(self.lib.ifx_argmax(_ptr(logits), _ptr(out), R, V, _stream()), "argmax")
         self.launches += 1
         return out

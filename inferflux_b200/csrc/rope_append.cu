@@ -1,7 +1,9 @@
 // Bias add, rotation of queries and keys, and the write of keys and values into
 // the paged cache, in one launch.
 //
-// qkv [T, (nq + 2 nkv) d] holds the stacked projections.  For every token t and
+// qkv [T, (nq + 2 nkv) d] holds the stacked projections, either in the run's dtype
+// or as float32 partial sums [splits, T, width] of a K-split product, which are
+// added here in split order before the bias.  For every token t and
 // head: add the bias in float32 (if any), rotate the first `rot` elements of q and
 // k heads by angle = position * inv_freq in float32 (precise sincosf), write q to
 // q_out [T, nq d], the rotated key and the raw value to the cache page that holds
@@ -14,7 +16,8 @@
 namespace ifx {
 
 template <typename T>
-__global__ void rope_append_kernel(const T* __restrict__ qkv, const float* __restrict__ bias,
+__global__ void rope_append_kernel(const T* __restrict__ qkv, const float* __restrict__ qkv_partial, int num_splits,
+                                   size_t split_stride, const float* __restrict__ bias,
                                    const float* __restrict__ inv_freq, int rot, int interleaved,
                                    const int* __restrict__ positions, const int* __restrict__ token_req,
                                    const int* __restrict__ req_slot, const int* __restrict__ block_table,
@@ -23,7 +26,15 @@ __global__ void rope_append_kernel(const T* __restrict__ qkv, const float* __res
   const int t = blockIdx.x;
   const int head = blockIdx.y;                      // [0, nq) q, [nq, nq+nkv) k, then v
   const int width = (nq + 2 * nkv) * d;
-  const T* src = qkv + (size_t)t * width + (size_t)head * d;
+  const size_t src_off = (size_t)t * width + (size_t)head * d;
+  const T* src = qkv ? qkv + src_off : nullptr;
+  const float* psrc = qkv_partial ? qkv_partial + src_off : nullptr;
+  auto load = [&](int e) -> float {
+    if (psrc == nullptr) return to_f32(src[e]);
+    float v = 0.0f;
+    for (int s = 0; s < num_splits; ++s) v += psrc[(size_t)s * split_stride + e];
+    return v;
+  };
   const float* b = bias ? bias + (size_t)head * d : nullptr;
   const int pos = positions[t];
 
@@ -54,7 +65,7 @@ __global__ void rope_append_kernel(const T* __restrict__ qkv, const float* __res
       e0 = rot + 2 * (j - half_rot);
       e1 = e0 + 1;
     }
-    float a = to_f32(src[e0]), c = to_f32(src[e1]);
+    float a = load(e0), c = load(e1);
     if (b) {
       a += b[e0];
       c += b[e1];
@@ -76,7 +87,7 @@ __global__ void rope_append_kernel(const T* __restrict__ qkv, const float* __res
 
 using namespace ifx;
 
-extern "C" int ifx_rope_append(const void* qkv, const float* bias, const float* inv_freq, int rot,
+extern "C" int ifx_rope_append(const void* qkv, const float* qkv_partial, int num_splits, const float* bias, const float* inv_freq, int rot,
                                int interleaved, const int* positions, const int* token_req,
                                const int* req_slot, const int* block_table, int max_blocks, int page_size,
                                int num_pages, void* kv_pool, void* q_out, int num_tokens, int nq, int nkv,
@@ -86,15 +97,18 @@ extern "C" int ifx_rope_append(const void* qkv, const float* bias, const float* 
   if (rot > 0 && inv_freq == nullptr) return IFX_E_BADARG;
   if (write_cache && (page_size <= 0 || max_blocks <= 0 || kv_pool == nullptr)) return IFX_E_BADARG;
   if (nq + 2 * nkv > 65535) return IFX_E_TOOBIG;
+  if ((qkv == nullptr) == (qkv_partial == nullptr)) return IFX_E_BADARG;
+  if (qkv_partial != nullptr && num_splits <= 0) return IFX_E_BADARG;
+  const size_t split_stride = (size_t)num_tokens * (nq + 2 * nkv) * d;
   dim3 grid(num_tokens, nq + 2 * nkv);
   int threads = d / 2 >= 64 ? 64 : 32;
   if (dtype == IFX_DT_F32)
     rope_append_kernel<float><<<grid, threads, 0, stream>>>(
-        (const float*)qkv, bias, inv_freq, rot, interleaved, positions, token_req, req_slot, block_table,
+        (const float*)qkv, qkv_partial, num_splits, split_stride, bias, inv_freq, rot, interleaved, positions, token_req, req_slot, block_table,
         max_blocks, page_size, num_pages, (float*)kv_pool, (float*)q_out, nq, nkv, d, write_cache);
   else if (dtype == IFX_DT_BF16)
     rope_append_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>(
-        (const __nv_bfloat16*)qkv, bias, inv_freq, rot, interleaved, positions, token_req, req_slot,
+        (const __nv_bfloat16*)qkv, qkv_partial, num_splits, split_stride, bias, inv_freq, rot, interleaved, positions, token_req, req_slot,
         block_table, max_blocks, page_size, num_pages, (__nv_bfloat16*)kv_pool, (__nv_bfloat16*)q_out, nq,
         nkv, d, write_cache);
   else

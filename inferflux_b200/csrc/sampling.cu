@@ -61,6 +61,43 @@ __global__ void argmax_kernel(const float* __restrict__ logits, int* __restrict_
   if (threadIdx.x == 0) out[blockIdx.x] = b.i;
 }
 
+// Argmax of long rows over many blocks: block (row, chunk) finds the best of its
+// slice, the block that finishes a row last (a ticket per row, reset for the next
+// launch) picks among the chunk results, the lower index winning ties.
+__global__ void argmax_chunks_kernel(const float* __restrict__ logits, int* __restrict__ out, int vocab, int chunks,
+                                     float* __restrict__ part_val, int* __restrict__ part_idx,
+                                     int* __restrict__ tickets) {
+  __shared__ ArgBest scratch[32];
+  __shared__ int is_last;
+  const int row = blockIdx.x, chunk = blockIdx.y;
+  const int per = (vocab + chunks - 1) / chunks;
+  const int begin = min(vocab, chunk * per), end = min(vocab, begin + per);
+  const float* base = logits + (size_t)row * vocab;
+  ArgBest b = block_argmax(base + begin, end - begin, 1.0f, scratch);
+  if (threadIdx.x == 0) {
+    part_val[row * chunks + chunk] = end > begin ? b.v : -INFINITY;
+    part_idx[row * chunks + chunk] = begin + b.i;
+    __threadfence();
+    const int t = atomicAdd(&tickets[row], 1);
+    is_last = t == chunks - 1;
+    if (is_last) tickets[row] = 0;
+  }
+  __syncthreads();
+  if (!is_last || threadIdx.x >= 32) return;
+  __threadfence();
+  ArgBest best{-INFINITY, 0x7fffffff};
+  for (int c = threadIdx.x; c < chunks; c += 32) {
+    ArgBest o{__ldcg(&part_val[row * chunks + c]), __ldcg(&part_idx[row * chunks + c])};
+    best = better(best, o);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    ArgBest other{__shfl_xor_sync(0xffffffffu, best.v, o), __shfl_xor_sync(0xffffffffu, best.i, o)};
+    best = better(best, other);
+  }
+  if (threadIdx.x == 0) out[row] = best.i == 0x7fffffff ? 0 : best.i;
+}
+
 // ------------------------------------------------------------------ penalties
 // For each distinct recent token of a row (tokens[r, i], counts[r, i] > 0):
 // logit = logit > 0 ? logit / rep : logit * rep;  logit -= freq * count;  logit -= pres.
@@ -243,6 +280,18 @@ int ifx_argmax(const float* logits, int* out, int rows, int vocab, cudaStream_t 
   if (rows <= 0) return 0;
   if (vocab <= 0) return IFX_E_BADARG;
   argmax_kernel<<<rows, 1024, 0, stream>>>(logits, out, vocab);
+  IFX_CHECK_LAUNCH();
+  return 0;
+}
+
+// scratch: part_val float32 [rows, chunks], part_idx int32 [rows, chunks], tickets int32 [rows]
+// (zero before the first call; the kernel leaves them zero).
+int ifx_argmax_chunks(const float* logits, int* out, int rows, int vocab, int chunks, float* part_val, int* part_idx,
+                      int* tickets, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (vocab <= 0 || chunks <= 0 || chunks > 1024) return IFX_E_BADARG;
+  dim3 grid(rows, chunks);
+  argmax_chunks_kernel<<<grid, 256, 0, stream>>>(logits, out, vocab, chunks, part_val, part_idx, tickets);
   IFX_CHECK_LAUNCH();
   return 0;
 }

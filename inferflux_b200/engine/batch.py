@@ -34,8 +34,10 @@ class StepContext:
     batch), cu_seqlens[R+1] (span boundaries in the flat arrays), kv_lens[R]
     (tokens stored once the step is done), req_slot[R] (row of the block tables and
     of the state tensors), logit_rows[W] (flat token indices whose logits are
-    wanted), decode_rows[D] (flat indices of spans of one token), prefill_tiles[P,4]
-    (request, first flat row, rows, first position) for longer spans.
+    wanted), decode_rows[D] (flat indices of spans of one token), decode_meta[D,4]
+    (flat index, position, slot, 0: what the decode attention kernel needs of a token,
+    in one 16-byte load), prefill_tiles[P,4] (request, first flat row, rows, first
+    position) for longer spans.
     """
 
     def __init__(self, kernels, dtype, device):
@@ -63,7 +65,7 @@ class StepContext:
         entries of group g that changed since the last step."""
         ctx = cls(kernels, dtype, device)
         token_ids, positions, token_req, cu, kv_lens = [], [], [], [0], []
-        logit_rows, decode_rows, tiles = [], [], []
+        logit_rows, decode_rows, decode_meta, tiles = [], [], [], []
         for r, (e, start) in enumerate(zip(entries, starts)):
             n = len(e.tokens)
             if n == 0:
@@ -80,6 +82,7 @@ class StepContext:
                 logit_rows.append(base + int(w))
             if n == 1:
                 decode_rows.append(base)
+                decode_meta.extend((base, start, int(slots[r]), 0))
             else:
                 for off in range(0, n, PREFILL_TILE):
                     tiles.append((r, base + off, min(PREFILL_TILE, n - off), start + off))
@@ -98,7 +101,7 @@ class StepContext:
         sections: Dict[str, List[int]] = {
             "token_ids": token_ids, "positions": positions, "token_req": token_req,
             "cu_seqlens": cu, "kv_lens": kv_lens, "req_slot": list(slots),
-            "logit_rows": logit_rows, "decode_rows": decode_rows,
+            "logit_rows": logit_rows, "decode_rows": decode_rows, "decode_meta": decode_meta,
             "prefill_tiles": [v for t in tiles for v in t],
         }
         for g, ups in enumerate(table_updates):
@@ -128,13 +131,14 @@ class StepContext:
         return ctx
 
     _CORE = ("token_ids", "positions", "token_req", "cu_seqlens", "kv_lens", "req_slot", "logit_rows",
-             "decode_rows", "prefill_tiles")
+             "decode_rows", "decode_meta", "prefill_tiles")
 
     def _bind(self, buffer):
         for name in self._CORE:
             off, n = self._offsets[name]
             setattr(self, name, buffer[off:off + n])
         self.prefill_tiles = self.prefill_tiles.view(-1, 4)
+        self.decode_meta = self.decode_meta.view(-1, 4)
 
     def layout_key(self):
         """Two steps with the same key have their arrays at the same offsets."""

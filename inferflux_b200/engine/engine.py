@@ -151,6 +151,8 @@ class Engine:
             self.stats.d2h_bytes += 4 * len(sampled)
         self.stats.h2d_bytes += self.runner.last_ctx.meta_bytes
         self.stats.steps += 1
+        if self.stats.steps % 32 == 1 and hasattr(self.kernels, "check_errors"):
+            self.kernels.check_errors()                     # a kernel whose bounded wait ran out says so here
         self.stats.prompt_tokens += sum(e.count for e in plan.entries if e.count > 1 or not e.request.output)
         self.stats.generated_tokens += len(sampled)
         self.stats.preemptions = self.scheduler.num_preemptions

@@ -80,8 +80,8 @@ class Attention(Mixer):
     # --------------------------------------------------------------------- forward
     def forward(self, h, ctx, cache):
         k = ctx.kernels
-        qkv = k.linear(h, self.w_qkv)                                        # [T, (nq + 2 nkv) d]
+        qkv = k.linear(h, self.w_qkv, allow_partial=True)                    # [T, (nq + 2 nkv) d], maybe in K slices
         rotary = self.position.rotary(h.device) if self.position is not None else None
         q = k.rope_append(qkv, self.b_qkv, rotary, self.nq, self.nkv, self.d, ctx, cache)   # [T, nq d]
         a = k.attention(q, self.nq, self.nkv, self.d, self.window, self.scale, ctx, cache)  # [T, nq d]
-        return k.linear(a, self.w_o)
+        return k.linear(a, self.w_o, allow_partial=True)

@@ -13,7 +13,10 @@ does its work through the kernel table of the step (`ctx.kernels`).
 
 `x` is the float32 residual stream [tokens, hidden]; `h` and `y` are in the dtype
 the run computes in.  `pending` is a delta that has not been added to `x` yet, so
-that the next norm can add it and normalise in one kernel.
+that the next norm can add it and normalise in one kernel.  A delta (and so a `y`)
+may be a plain tensor or what `ctx.kernels.linear(..., allow_partial=True)` returned:
+the partial sums of a K-split product, which `add_rmsnorm`, `residual_add` and
+`rope_append` add in the same pass; `ctx.kernels.materialize(y)` gives the tensor.
 """
 from __future__ import annotations
 

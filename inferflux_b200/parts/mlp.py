@@ -34,6 +34,5 @@ class SwiGLU(FeedForward):
 
     def forward(self, h, ctx):
         k = ctx.kernels
-        gate_up = k.linear(h, self.w_gate_up)            # [T, 2I]: gate | up
-        act = k.silu_mul(gate_up)                        # [T, I]
-        return k.linear(act, self.w_down)
+        act = k.linear_swiglu(h, self.w_gate_up)         # [T, I] = silu(h Wg^T) * (h Wu^T)
+        return k.linear(act, self.w_down, allow_partial=True)

@@ -49,13 +49,19 @@ class PlainKernels:
             table.view(-1)[index.long()] = value
 
     # ------------------------------------------------------------------ linear
-    def linear(self, a, w, bias=None, out_dtype=None):
+    def linear(self, a, w, bias=None, out_dtype=None, allow_partial=False):
         y = a.to(self.acc) @ w.to(self.acc).t()
         if bias is not None:
             y = y + bias.to(self.acc)
         return y.to(out_dtype or a.dtype)
 
     linear_generic = linear
+
+    def linear_swiglu(self, a, w_gate_up):
+        return self.silu_mul(self.linear(a, w_gate_up))
+
+    def materialize(self, value, bias=None):
+        return value if bias is None else value + bias.to(value.dtype)
 
     # --------------------------------------------------------------- attention
     def rope_append(self, qkv, bias, rotary, nq, nkv, d, ctx, cache):
@@ -84,8 +90,8 @@ class PlainKernels:
             slot = ctx.req_slot.long()[ctx.token_req.long()]
             page = cache.block_table[slot, pos // P].long()
             off = pos % P
-            cache.kv[page, 0, :, off, :] = x[:, nq:nq + nkv, :]
-            cache.kv[page, 1, :, off, :] = x[:, nq + nkv:, :]
+            cache.kv[page, 0, :, off, :] = x[:, nq:nq + nkv, :].to(cache.kv.dtype)
+            cache.kv[page, 1, :, off, :] = x[:, nq + nkv:, :].to(cache.kv.dtype)
         return x[:, :nq, :].reshape(T, nq * d).contiguous()
 
     def attention(self, q, nq, nkv, d, window, scale, ctx, cache):

@@ -93,6 +93,67 @@ def test_gemm_bfloat16(cuda_kernels, M, N, K, out_dtype):
     close(cuda_kernels.linear_generic(a, w, out_dtype=out_dtype), want, atol=1e-4 * math.sqrt(K), rtol=rtol)
 
 
+@pytest.mark.parametrize("M,N,K", [(1, 128, 64), (8, 256, 512), (17, 1000, 200), (33, 300, 328), (64, 3584, 1024),
+                                   (100, 130, 72), (128, 520, 4104), (5, 4608, 3584)])
+def test_gemm_tcgen05_few_rows(cuda_kernels, M, N, K):
+    """The weight-streaming tensor-core product: plain store (bfloat16 and float32 out, with
+    bias), K split into partial sums and their consumers, and the fused silu(gate) * up."""
+    from inferflux_b200.csrc import PartialSum
+    a = rnd(M, K, dtype=torch.bfloat16, seed=20, scale=0.5)
+    w = rnd(N, K, dtype=torch.bfloat16, seed=21, scale=0.1)
+    b = rnd(N, seed=22)
+    want = a.double() @ w.double().t()
+    tol = 1e-4 * math.sqrt(K)
+    close(cuda_kernels.linear_skinny(a, w, None, out_dtype=torch.bfloat16), want, atol=tol, rtol=2 ** -8)
+    close(cuda_kernels.linear_skinny(a, w, b, out_dtype=torch.float32), want + b.double(), atol=tol, rtol=1e-5)
+    kblocks = -(-K // 64)
+    for splits in sorted({1, min(3, kblocks), min(10, kblocks)}):
+        parts = cuda_kernels.linear_skinny(a, w, None, splits=splits, mode=1)
+        assert parts.shape == (splits, M, N)
+        close(parts.double().sum(0), want, atol=tol, rtol=1e-5)
+        ps = PartialSum(parts, torch.bfloat16)
+        close(cuda_kernels.materialize(ps, b), want + b.double(), atol=tol, rtol=2 ** -8)
+        x = rnd(M, N, seed=23)
+        x1, x2 = x.clone(), x.clone()
+        cuda_kernels.residual_add(x1, ps)
+        close(x1, x.double() + want, atol=tol, rtol=1e-5)
+        wn = 1 + rnd(N, seed=24, scale=0.1)
+        got = cuda_kernels.add_rmsnorm(x2, ps, wn, 1e-5, torch.bfloat16)
+        ref = PlainKernels(wide=True).rmsnorm(x.double() + want, wn, 1e-5, torch.float64)
+        assert torch.equal(x1, x2)
+        close(got, ref, atol=1e-3, rtol=2 ** -7)
+    if N % 2 == 0:
+        half = N // 2
+        g, u = want[:, :half], want[:, half:]
+        got = cuda_kernels.linear_skinny(a, w, None, mode=2, n_out=half, up_row_offset=half)
+        close(got, g / (1 + torch.exp(-g)) * u, atol=tol, rtol=2 ** -7)
+        close(cuda_kernels.linear_swiglu(a, w), g / (1 + torch.exp(-g)) * u, atol=tol, rtol=2 ** -7)
+    # the routing in `linear`: few rows go to this kernel, with or without partial sums
+    r = cuda_kernels.linear(a, w, allow_partial=True)
+    close(cuda_kernels.materialize(r), want, atol=tol, rtol=2 ** -8)
+    cuda_kernels.check_errors()
+
+
+def test_rope_append_from_partial_sums(cuda_kernels):
+    from inferflux_b200.csrc import PartialSum
+    from inferflux_b200.parts.base import RotaryTable
+    nq, nkv, d, page = 6, 2, 32, 8
+    lens, spans = [40, 9], [7, 1]
+    ctx, cache, slots = make_cache_case(torch.bfloat16, nkv, d, page, lens, spans, num_pages=12, seed=1)
+    T, width = ctx.num_tokens, (nq + 2 * nkv) * d
+    parts = rnd(3, T, width, seed=2)
+    bias = rnd(width, seed=3)
+    inv = (1.0 / (1e4 ** (torch.arange(0, d, 2, dtype=torch.float32) / d))).to(DEV)
+    rotary = RotaryTable(inv, d, False)
+    kv0 = cache.kv.clone()
+    q1 = cuda_kernels.rope_append(PartialSum(parts, torch.bfloat16), bias, rotary, nq, nkv, d, ctx, cache)
+    kv1 = cache.kv.clone()
+    cache.kv = kv0
+    q2 = PlainKernels(wide=True).rope_append(parts.sum(0).double(), bias, rotary, nq, nkv, d, ctx, cache)
+    close(q1, q2, atol=2e-2, rtol=2 ** -7)
+    close(kv1, cache.kv, atol=2e-2, rtol=2 ** -7)
+
+
 # ---------------------------------------------------------------------- attention
 
 class _Ctx:
@@ -132,6 +193,8 @@ def make_cache_case(dtype, nkv, d, page, lens, spans, num_pages, seed, shuffle=T
                 tiles.append([r, base + off, min(64, s_ - off), n - s_ + off])
         base += s_
     ctx.decode_rows = torch.tensor(decode_rows, dtype=torch.int32, device=DEV)
+    ctx.decode_meta = torch.tensor([[t, positions[t], slots[token_req[t]], 0] for t in decode_rows],
+                                   dtype=torch.int32, device=DEV).view(-1, 4)
     ctx.prefill_tiles = torch.tensor(tiles, dtype=torch.int32, device=DEV).view(-1, 4)
     ctx.num_decode_rows, ctx.num_prefill_tiles = len(decode_rows), len(tiles)
     ctx.max_kv_len = max(lens)

@@ -49,7 +49,7 @@ def test_norm_ffn_embedding_head_alone(cuda_kernels, dtype, tol):
                   _rnd(H, I, seed=6, scale=0.1).to(dtype))
     ffn.load({"gate_proj.weight": wg, "up_proj.weight": wu, "down_proj.weight": wd}, dtype, DEV)
     h = x.to(dtype)
-    got = ffn.forward(h.to(DEV), ctx).float().cpu()
+    got = cuda_kernels.materialize(ffn.forward(h.to(DEV), ctx)).float().cpu()
     want = plain_qwen2.swiglu_mlp(h.double(), wg.double(), wu.double(), wd.double())
     assert float((got - want).abs().max()) < tol * max(1.0, float(want.abs().max()))
     # embedding and head (tied)
@@ -108,7 +108,8 @@ def test_attention_part_alone(cuda_kernels, dtype, tol):
                                     cache.drain_table_updates())
             for g, (idx, page) in zip(cache.groups, ctx.table_updates):
                 cuda_kernels.scatter_i32(g.table, idx, page)
-            outs.append(mixer.forward(h[pos:pos + n].to(DEV).contiguous(), ctx, cache.view(ScheduleEntry(0, 0))))
+            outs.append(cuda_kernels.materialize(mixer.forward(h[pos:pos + n].to(DEV).contiguous(), ctx,
+                                                               cache.view(ScheduleEntry(0, 0)))))
             cache.commit("r", pos + n)
             pos += n
         got = torch.cat(outs).float().cpu()
