@@ -324,3 +324,47 @@ int ifx_sample(const float* logits, float* probs, const float* temperature, cons
 }
 
 }  // extern "C"
+
+// --------------------------------------------------------------- no allocation
+// See no_alloc.h.  The scratch of the many-block argmax as a fixed array in the
+// library image, for callers that cannot allocate: [rows x chunks] best values, then
+// [rows x chunks] best indices, then one ticket per row (padded to 8 bytes a row).
+#include "no_alloc.h"
+
+static __device__ __align__(256) unsigned char g_no_alloc_scratch[IFX_NO_ALLOC_SCRATCH_BYTES];
+
+namespace {
+constexpr int kNoAllocMaxDevices = 64;
+// Device address of g_no_alloc_scratch per device; in host code the array's name is only a
+// handle for cudaGetSymbolAddress, never a pointer a kernel may be given.
+void* g_no_alloc_ptr[kNoAllocMaxDevices] = {};
+}  // namespace
+
+extern "C" int ifx_argmax_no_alloc(const float* logits, int* out, int rows, int vocab, cudaStream_t stream) {
+  if (rows == 0) return 0;
+  if (logits == nullptr || out == nullptr || rows < 0 || vocab <= 0 || vocab > (1 << 30)) return IFX_E_BADARG;
+  if (rows > IFX_NO_ALLOC_MAX_ROWS) return IFX_E_TOOBIG;
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= kNoAllocMaxDevices) return IFX_E_TOOBIG;
+  if (g_no_alloc_ptr[dev] == nullptr) {                 // first call on this device: look the address up
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_no_alloc_scratch);
+    if (e != cudaSuccess) return (int)e;
+    if (p == nullptr) return IFX_E_BADARG;
+    g_no_alloc_ptr[dev] = p;
+  }
+  unsigned char* base = static_cast<unsigned char*>(g_no_alloc_ptr[dev]);
+  float* part_val = reinterpret_cast<float*>(base);
+  int* part_idx = reinterpret_cast<int*>(base + (size_t)IFX_NO_ALLOC_MAX_ROWS * IFX_NO_ALLOC_CHUNKS * 4);
+  int* tickets = reinterpret_cast<int*>(base + (size_t)IFX_NO_ALLOC_MAX_ROWS * IFX_NO_ALLOC_CHUNKS * 8);
+  // the tickets must start at zero whatever an earlier (perhaps failed) call left behind
+  e = cudaMemsetAsync(tickets, 0, (size_t)rows * sizeof(int), stream);
+  if (e != cudaSuccess) return (int)e;
+  dim3 grid(rows, IFX_NO_ALLOC_CHUNKS);
+  ifx::argmax_chunks_kernel<<<grid, 256, 0, stream>>>(logits, out, vocab, IFX_NO_ALLOC_CHUNKS, part_val, part_idx,
+                                                      tickets);
+  IFX_CHECK_LAUNCH();
+  return 0;
+}
