@@ -51,6 +51,10 @@ class _Request:
     generation: int
     length: int = 0                                              # tokens whose keys/values are stored
     blocks: List[Dict[int, int]] = field(default_factory=list)   # per group: logical block -> page
+    # per group: blocks [lo, hi) are held (blocks are taken upward without gaps inside what is still
+    # needed, and given back from below), so counting what a step needs is O(1)
+    lo: List[int] = field(default_factory=list)
+    hi: List[int] = field(default_factory=list)
 
 
 class _Group:
@@ -140,7 +144,9 @@ class CacheManager:
         for st in self.state:
             if st is not None:
                 st[slot].zero_()
-        self._requests[rid] = _Request(rid, slot, self._generation[slot], 0, [dict() for _ in self.groups])
+        n = len(self.groups)
+        self._requests[rid] = _Request(rid, slot, self._generation[slot], 0, [dict() for _ in self.groups],
+                                       [0] * n, [0] * n)
         return slot
 
     def free(self, rid, generation: Optional[int] = None) -> None:
@@ -171,9 +177,9 @@ class CacheManager:
         req = self._requests[rid]
         last = -(-new_len // self.page_size)
         need = []
-        for g, held in zip(self.groups, req.blocks):
+        for gi, g in enumerate(self.groups):
             first = self._first_needed_block(g, req.length)
-            need.append(sum(1 for b in range(first, last) if b not in held))
+            need.append(max(0, last - max(first, req.hi[gi])))
         return need
 
     def pages_needed_fresh(self, new_len: int) -> List[int]:
@@ -203,28 +209,35 @@ class CacheManager:
                 raise OutOfPages(f"request {rid!r} needs {need} pages per group to reach {new_len} tokens, "
                                  f"free: {self.free_pages()}")
         last = -(-new_len // self.page_size)
-        for g, held in zip(self.groups, req.blocks):
+        for gi, (g, held) in enumerate(zip(self.groups, req.blocks)):
             first = self._first_needed_block(g, req.length)
-            wanted = [b for b in range(first, last) if b not in held]
-            pages = g.alloc.allocate(len(wanted), owner=rid)
-            for b, p in zip(wanted, pages):
+            start = max(first, req.hi[gi])
+            if start >= last:
+                continue
+            pages = g.alloc.allocate(last - start, owner=rid)
+            for b, p in zip(range(start, last), pages):
                 held[b] = p
                 g.updates.append((req.slot * self.max_blocks + b, p))
+            if not held or req.hi[gi] <= req.lo[gi]:
+                req.lo[gi] = start
+            req.hi[gi] = last
 
     def commit(self, rid, new_len: int) -> None:
         """The step has stored positions up to new_len - 1; pages that a window has
         moved past are given back."""
         req = self._requests[rid]
         req.length = new_len
-        for g, held in zip(self.groups, req.blocks):
+        for gi, (g, held) in enumerate(zip(self.groups, req.blocks)):
             if g.spec.window is None:
                 continue
-            first = self._first_needed_block(g, new_len)
-            dead = [b for b in held if b < first]
-            if dead:
-                g.alloc.release([held[b] for b in dead], owner=rid)
-                for b in dead:
-                    del held[b]
+            first = min(self._first_needed_block(g, new_len), req.hi[gi])
+            if req.lo[gi] < first:
+                dead = [b for b in range(req.lo[gi], first) if b in held]
+                if dead:
+                    g.alloc.release([held[b] for b in dead], owner=rid)
+                    for b in dead:
+                        del held[b]
+                req.lo[gi] = first
 
     def drain_table_updates(self) -> List[List[Tuple[int, int]]]:
         """Per group, the (flat index, page) pairs that the device block table has

@@ -28,7 +28,10 @@
 // larger than 16 in decoding, are refused (the caller then uses the generic kernel).
 #include <cooperative_groups.h>
 
+#include <unordered_map>
+
 #include "common.cuh"
+#include "ptx_sm100.cuh"
 
 namespace ifx {
 
@@ -512,6 +515,356 @@ attn_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kv_pool,
   cluster.sync();                                       // nobody leaves while its shared memory is being read
 }
 
+// ------------------------------------------- decoded tokens, pages fetched by TMA
+// The same work as attn_decode_kernel for page sizes that are multiples of 16 and
+// head sizes that are multiples of 64: a 16-key tile lies inside one page, so each
+// warp's lane 0 fetches it with cp.async.bulk.tensor boxes [16 keys x 64 elements]
+// (128-byte swizzle) from the pool seen as a matrix [pages * 2 * nkv * page_size, D],
+// and the warp waits on the stage's mbarrier.  No per-lane address arithmetic, no
+// padding: ldmatrix reads the swizzled tiles without bank conflicts.
+template <int D, int STAGES>
+__global__ void __launch_bounds__(128)
+attn_decode_tma_kernel(const __grid_constant__ CUtensorMap pool_map, const bf16* __restrict__ q,
+                       const int* __restrict__ block_table, const int4* __restrict__ decode_meta,
+                       bf16* __restrict__ out, int nq, int nkv, int page_size, int page_shift, int max_blocks,
+                       int num_pages, int window, float scale_log2, int tbl_cap, int* __restrict__ error_flag) {
+  constexpr int LDS = D + 8;
+  constexpr int CPR = D / 8;
+  constexpr int HALVES = D / 64;
+  constexpr int TILE_BYTES = 16 * D * 2;                // one K or V tile: HALVES boxes of 2 KB
+  constexpr int STAGE_BYTES = 2 * TILE_BYTES;
+  constexpr int STAGE_BYTES_ALL = 4 * STAGES * STAGE_BYTES;
+  constexpr int MERGE_BYTES = (4 * 16 * D + 2 * 4 * 16) * 4;
+  constexpr int FIN_BYTES = (16 * D + 32) * 4;
+  constexpr int WORK_BYTES = STAGE_BYTES_ALL > MERGE_BYTES + FIN_BYTES ? STAGE_BYTES_ALL : MERGE_BYTES + FIN_BYTES;
+  extern __shared__ unsigned char smem_dyn[];
+  unsigned char* stage_base =
+      reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~(uintptr_t)1023);
+  float* fin_o = reinterpret_cast<float*>(stage_base + MERGE_BYTES);     // [16][D], behind the warps' merge buffers
+  float* fin_m = fin_o + 16 * D;
+  float* fin_l = fin_m + 16;
+  bf16* q_s = reinterpret_cast<bf16*>(stage_base + WORK_BYTES);           // [16][LDS]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(q_s + 16 * LDS);          // [4 warps][STAGES]
+  int* tbl_s = reinterpret_cast<int*>(bars + 4 * STAGES);                // [tbl_cap]
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int item = blockIdx.x, g = blockIdx.y, split = blockIdx.z, num_splits = gridDim.z;
+  const int G = nq / nkv;
+  const int4 meta = decode_meta[item];
+  const int t = meta.x;
+  const int pos = meta.y;
+  const int* table_g = block_table + (size_t)meta.z * max_blocks;
+  const int* table = table_g;
+  int blk_base = 0;
+
+  const int kfirst = window > 0 ? max(0, pos - window + 1) : 0;
+  const int kstart = kfirst & ~15;                      // tiles start on multiples of 16 so that one lies in one page
+  const int kend = pos + 1;
+  const int per_split = (((kend - kstart + num_splits - 1) / num_splits) + 63) / 64 * 64;
+  const int k0 = kstart + split * per_split;
+  const int k1 = min(kend, k0 + per_split);
+  if (k0 < k1) {
+    const int b0 = k0 >> page_shift, b1 = (k1 - 1) >> page_shift;
+    if (b1 - b0 + 1 <= tbl_cap) {
+      for (int i = tid; i <= b1 - b0; i += 128) tbl_s[i] = table_g[b0 + i];
+      table = tbl_s;
+      blk_base = b0;
+    }
+  }
+  if (tid == 0) {
+    for (int i = 0; i < 4 * STAGES; ++i) mbar_init(smem_addr(bars + i), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  for (int i = tid; i < 16 * CPR; i += 128) {
+    const int row = i / CPR, c = i % CPR;
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (row < G) v = *reinterpret_cast<const uint4*>(q + ((size_t)t * nq + g * G + row) * D + c * 8);
+    *reinterpret_cast<uint4*>(q_s + row * LDS + c * 8) = v;
+  }
+  __syncthreads();
+  uint32_t qf[D / 16][4];
+#pragma unroll
+  for (int kk = 0; kk < D / 16; ++kk) {
+    const int row = (lane & 7) + ((lane >> 3) & 1) * 8, col = kk * 16 + (lane >> 4) * 8;
+    ldmatrix_x4(qf[kk], smem_u32(q_s + row * LDS + col));
+  }
+
+  const uint32_t my_stage0 = smem_addr(stage_base) + warp * STAGES * STAGE_BYTES;
+  const uint32_t my_bar0 = smem_addr(bars + warp * STAGES);
+  auto issue_tile = [&](int base, int stage) {           // lane 0 only: keys base .. base + 15
+    int page = table[(base >> page_shift) - blk_base];
+    if (page < 0 || page >= num_pages) page = 0;
+    const int off = base & (page_size - 1);
+    const int yk = ((page * 2) * nkv + g) * page_size + off;
+    const int yv = ((page * 2 + 1) * nkv + g) * page_size + off;
+    const uint32_t dst = my_stage0 + stage * STAGE_BYTES, bar = my_bar0 + 8 * stage;
+    mbar_expect_tx(bar, STAGE_BYTES);
+#pragma unroll
+    for (int h = 0; h < HALVES; ++h) {
+      tma_load_2d(dst + h * 2048, &pool_map, h * 64, yk, bar);
+      tma_load_2d(dst + TILE_BYTES + h * 2048, &pool_map, h * 64, yv, bar);
+    }
+  };
+  // byte offset of the 16-byte chunk holding elements [col, col + 8) of row `row` in a swizzled tile
+  auto tile_off = [](int row, int col) -> uint32_t {
+    return (uint32_t)((col >> 6) * 2048 + row * 128 + ((((col & 63) >> 3) ^ (row & 7)) << 4));
+  };
+
+  float o[D / 8][4];
+#pragma unroll
+  for (int i = 0; i < D / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
+  float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.0f, l_hi = 0.0f;
+
+  const int first_base = k0 + warp * 16;
+  const int stride = 64;
+  if (lane == 0) {
+#pragma unroll
+    for (int s = 0; s < STAGES - 1; ++s)
+      if (first_base + s * stride < k1) issue_tile(first_base + s * stride, s);
+  }
+  int n_iter = 0;
+  bool ok = true;
+  for (int base = first_base; base < k1; base += stride, ++n_iter) {
+    const int stage = n_iter % STAGES;
+    const int ahead = base + (STAGES - 1) * stride;
+    if (lane == 0 && ahead < k1) {
+      fence_proxy_async_smem();                           // the stage's last readers (ldmatrix) come before the copy
+      issue_tile(ahead, (n_iter + STAGES - 1) % STAGES);
+    }
+    ok = mbar_wait(my_bar0 + 8 * stage, (n_iter / STAGES) & 1);
+    if (!ok) break;
+    const uint32_t kt = my_stage0 + stage * STAGE_BYTES, vt = kt + TILE_BYTES;
+    if (base + 16 > k1) {                                 // the range ends inside this tile: what lies behind it in
+      const int valid = k1 - base;                        // the page is someone's old data; never multiply by it
+      for (int i = lane; i < (16 - valid) * (D / 8); i += 32) {
+        const int row = valid + i / (D / 8), c = (i % (D / 8)) * 8;
+        asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(vt + tile_off(row, c)), "r"(0) : "memory");
+      }
+      __syncwarp();
+    }
+    float s[2][4];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.0f;
+#pragma unroll
+    for (int kk = 0; kk < D / 16; ++kk) {
+      uint32_t b[4];
+      const int row = (lane >> 4) * 8 + (lane & 7), col = kk * 16 + ((lane >> 3) & 1) * 8;
+      ldmatrix_x4(b, kt + tile_off(row, col));
+      mma_bf16(s[0], qf[kk], b[0], b[1]);
+      mma_bf16(s[1], qf[kk], b[2], b[3]);
+    }
+    float mx_lo = -INFINITY, mx_hi = -INFINITY;
+#pragma unroll
+    for (int n = 0; n < 2; ++n) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int key = base + n * 8 + 2 * (lane & 3) + (e & 1);
+        s[n][e] = (key < k1 && key >= kfirst) ? s[n][e] * scale_log2 : -INFINITY;
+      }
+      mx_lo = fmaxf(mx_lo, fmaxf(s[n][0], s[n][1]));
+      mx_hi = fmaxf(mx_hi, fmaxf(s[n][2], s[n][3]));
+    }
+    mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1));
+    mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
+    mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1));
+    mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
+    const float mn_lo = fmaxf(m_lo, mx_lo), mn_hi = fmaxf(m_hi, mx_hi);
+    // a tile in front of the window's first key may hold no valid key at all
+    const float mu_lo = mn_lo == -INFINITY ? 0.0f : mn_lo, mu_hi = mn_hi == -INFINITY ? 0.0f : mn_hi;
+    const float c_lo = exp2f(m_lo - mu_lo), c_hi = exp2f(m_hi - mu_hi);
+    m_lo = mn_lo;
+    m_hi = mn_hi;
+    l_lo *= c_lo;
+    l_hi *= c_hi;
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i) {
+      o[i][0] *= c_lo;
+      o[i][1] *= c_lo;
+      o[i][2] *= c_hi;
+      o[i][3] *= c_hi;
+    }
+    uint32_t pa[4];
+    {
+      const float e0 = exp2f(s[0][0] - mu_lo), e1 = exp2f(s[0][1] - mu_lo);
+      const float e2 = exp2f(s[0][2] - mu_hi), e3 = exp2f(s[0][3] - mu_hi);
+      const float f0 = exp2f(s[1][0] - mu_lo), f1 = exp2f(s[1][1] - mu_lo);
+      const float f2 = exp2f(s[1][2] - mu_hi), f3 = exp2f(s[1][3] - mu_hi);
+      l_lo += e0 + e1 + f0 + f1;
+      l_hi += e2 + e3 + f2 + f3;
+      pa[0] = pack_bf16(e0, e1);
+      pa[1] = pack_bf16(e2, e3);
+      pa[2] = pack_bf16(f0, f1);
+      pa[3] = pack_bf16(f2, f3);
+    }
+#pragma unroll
+    for (int d2 = 0; d2 < D / 16; ++d2) {
+      uint32_t b[4];
+      const int row = ((lane >> 3) & 1) * 8 + (lane & 7), col = d2 * 16 + (lane >> 4) * 8;
+      ldmatrix_x4_trans(b, vt + tile_off(row, col));
+      mma_bf16(o[2 * d2], pa, b[0], b[1]);
+      mma_bf16(o[2 * d2 + 1], pa, b[2], b[3]);
+    }
+    __syncwarp();
+  }
+  if (!ok) {
+    if (lane == 0) atomicExch(error_flag, 4);
+    // copies that were issued and not waited for must land before the block leaves
+    for (int n = n_iter + 1; n < n_iter + STAGES; ++n)
+      if (first_base + n * stride < k1) mbar_wait(my_bar0 + 8 * (n % STAGES), (n / STAGES) & 1);
+  }
+  l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1);
+  l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
+  l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1);
+  l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
+
+  // ---- merge the four warps in shared memory (the staging buffers are free now)
+  __syncthreads();
+  float* c_o = reinterpret_cast<float*>(stage_base);          // [4][16][D]
+  float* c_m = c_o + 4 * 16 * D;
+  float* c_l = c_m + 4 * 16;
+  {
+    const int r_lo = lane >> 2, r_hi = r_lo + 8;
+#pragma unroll
+    for (int n = 0; n < D / 8; ++n) {
+      const int col = n * 8 + 2 * (lane & 3);
+      c_o[(warp * 16 + r_lo) * D + col] = o[n][0];
+      c_o[(warp * 16 + r_lo) * D + col + 1] = o[n][1];
+      c_o[(warp * 16 + r_hi) * D + col] = o[n][2];
+      c_o[(warp * 16 + r_hi) * D + col + 1] = o[n][3];
+    }
+    if ((lane & 3) == 0) {
+      c_m[warp * 16 + r_lo] = m_lo;
+      c_m[warp * 16 + r_hi] = m_hi;
+      c_l[warp * 16 + r_lo] = l_lo;
+      c_l[warp * 16 + r_hi] = l_hi;
+    }
+  }
+  __syncthreads();
+  for (int idx = tid; idx < G * D; idx += 128) {
+    const int row = idx / D, dim = idx % D;
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) M = fmaxf(M, c_m[w * 16 + row]);
+    float O = 0.0f, L = 0.0f;
+    if (M != -INFINITY) {
+#pragma unroll
+      for (int w = 0; w < 4; ++w) {
+        const float f = exp2f(c_m[w * 16 + row] - M);
+        O += f * c_o[(w * 16 + row) * D + dim];
+        L += f * c_l[w * 16 + row];
+      }
+    }
+    if (num_splits == 1) {
+      out[((size_t)t * nq + g * G + row) * D + dim] = __float2bfloat16_rn(L > 0.0f ? O / L : 0.0f);
+    } else {
+      fin_o[row * D + dim] = O;
+      if (dim == 0) {
+        fin_m[row] = M;
+        fin_l[row] = L;
+      }
+    }
+  }
+  if (num_splits == 1) return;
+  cg::cluster_group cluster = cg::this_cluster();
+  cluster.sync();
+  const int DS = D / num_splits;
+  for (int idx = tid; idx < G * DS; idx += 128) {
+    const int row = idx / DS, dim = split * DS + idx % DS;
+    float ms[8], ls[8], os[8];
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+      if (c < num_splits) {
+        ms[c] = cluster.map_shared_rank(fin_m, c)[row];
+        ls[c] = cluster.map_shared_rank(fin_l, c)[row];
+        os[c] = cluster.map_shared_rank(fin_o, c)[row * D + dim];
+      } else {
+        ms[c] = -INFINITY;
+        ls[c] = os[c] = 0.0f;
+      }
+    }
+    float M = -INFINITY;
+#pragma unroll
+    for (int c = 0; c < 8; ++c) M = fmaxf(M, ms[c]);
+    float O = 0.0f, L = 0.0f;
+    if (M != -INFINITY) {
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        const float f = exp2f(ms[c] - M);
+        O += f * os[c];
+        L += f * ls[c];
+      }
+    }
+    out[((size_t)t * nq + g * G + row) * D + dim] = __float2bfloat16_rn(L > 0.0f ? O / L : 0.0f);
+  }
+  cluster.sync();
+}
+
+template <int D>
+int launch_decode_tma(const CUtensorMap& pool_map, const bf16* q, const int* block_table, const int4* decode_meta,
+                      bf16* out, int num_items, int nq, int nkv, int page_size, int page_shift, int max_blocks,
+                      int num_pages, int window, float scale_log2, int num_splits, int max_keys, int* error_flag,
+                      cudaStream_t stream) {
+  constexpr int STAGES = D <= 128 ? 3 : 2;
+  constexpr int stage_bytes = 4 * STAGES * 2 * 16 * D * 2;
+  constexpr int merge_bytes = (4 * 16 * D + 2 * 4 * 16) * 4;
+  constexpr int fin_bytes = (16 * D + 32) * 4;
+  constexpr int work_bytes = stage_bytes > merge_bytes + fin_bytes ? stage_bytes : merge_bytes + fin_bytes;
+  const int per_split = (((max_keys + 16 + num_splits - 1) / num_splits) + 63) / 64 * 64;
+  int tbl_cap = per_split / page_size + 2;
+  if (tbl_cap > 8192) tbl_cap = 0;
+  const int smem = 1024 + work_bytes + 16 * (D + 8) * 2 + 4 * STAGES * 8 + tbl_cap * 4;
+  static int configured = 0;
+  if (smem > configured) {
+    cudaError_t e = cudaFuncSetAttribute(attn_decode_tma_kernel<D, STAGES>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return (int)e;
+    configured = smem;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(num_items, nkv, num_splits);
+  cfg.blockDim = dim3(128);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 1;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = num_splits;
+  cfg.attrs = attr;
+  cfg.numAttrs = num_splits > 1 ? 1 : 0;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, attn_decode_tma_kernel<D, STAGES>, pool_map, q, block_table, decode_meta,
+                                     out, nq, nkv, page_size, page_shift, max_blocks, num_pages, window, scale_log2,
+                                     tbl_cap, error_flag);
+  if (e != cudaSuccess) return (int)e;
+  return 0;
+}
+
+// Tensor maps of cache pools (one per layer's pool), made once and kept.
+static int pool_map_for(CUtensorMap* out, const void* base, long long rows, int d) {
+  struct Key {
+    const void* base;
+    long long rows;
+    int d;
+    bool operator==(const Key& o) const { return base == o.base && rows == o.rows && d == o.d; }
+  };
+  struct Hash {
+    size_t operator()(const Key& k) const { return std::hash<const void*>()(k.base) ^ (size_t)k.rows * 31u ^ (size_t)k.d; }
+  };
+  static std::unordered_map<Key, CUtensorMap, Hash> cache;
+  static std::mutex mu;
+  std::lock_guard<std::mutex> lock(mu);
+  Key key{base, rows, d};
+  auto it = cache.find(key);
+  if (it == cache.end()) {
+    CUtensorMap m;
+    int rc = make_tensor_map_bf16(&m, base, rows, d, 16);
+    if (rc) return rc;
+    it = cache.emplace(key, m).first;
+  }
+  *out = it->second;
+  return 0;
+}
+
 template <int D>
 int launch_prefill(const bf16* q, const bf16* kv_pool, const int* block_table, const int* tiles, const int* req_slot,
                    bf16* out, int num_tiles, int nq, int nkv, int page_size, int page_shift, int max_blocks,
@@ -621,11 +974,12 @@ int ifx_attention_prefill_bf16(const void* q, const void* kv_pool, const int* bl
 }
 
 // decode_meta: int32 [num_items, 4] = (flat token row, position, request slot, unused).
+// error_flag: device int that the TMA variant sets if a bounded wait runs out (nullptr: cp.async variant only).
 // num_splits: 1, 2, 4 or 8 blocks (one cluster) share a token's key range; it must divide d.
 // max_keys: no token of the step sees more keys than this.
 int ifx_attention_decode_bf16(const void* q, const void* kv_pool, const int* block_table, const int* decode_meta,
                               void* out, int num_items, int nq, int nkv, int d, int page_size, int max_blocks,
-                              int num_pages, int window, float scale, int num_splits, int max_keys,
+                              int num_pages, int window, float scale, int num_splits, int max_keys, int* error_flag,
                               cudaStream_t stream) {
   if (num_items <= 0) return 0;
   if (nq <= 0 || nkv <= 0 || nq % nkv || nq / nkv > 16 || page_size <= 0 || max_blocks <= 0 || nkv > 65535 ||
@@ -635,6 +989,20 @@ int ifx_attention_decode_bf16(const void* q, const void* kv_pool, const int* blo
     return IFX_E_BADARG;
   const float scale_log2 = scale * 1.4426950408889634f;
   const int ps = shift_of(page_size);
+  if (ps >= 4 && d % 64 == 0 && error_flag != nullptr) {       // pages of 16, 32, ... tokens: the TMA kernel
+    CUtensorMap pool_map;
+    const long long rows = (long long)num_pages * 2 * nkv * page_size;
+    int rc = pool_map_for(&pool_map, kv_pool, rows, d);
+    if (rc) return rc;
+#define CALL_TMA(DD)                                                                                              \
+  return launch_decode_tma<DD>(pool_map, (const bf16*)q, block_table, (const int4*)decode_meta, (bf16*)out,       \
+                               num_items, nq, nkv, page_size, ps, max_blocks, num_pages, window, scale_log2,      \
+                               num_splits, max_keys, error_flag, stream)
+    if (d == 64) CALL_TMA(64);
+    if (d == 128) CALL_TMA(128);
+    if (d == 256) CALL_TMA(256);
+#undef CALL_TMA
+  }
 #define CALL(DD)                                                                                                  \
   launch_decode<DD>((const bf16*)q, (const bf16*)kv_pool, block_table, (const int4*)decode_meta, (bf16*)out,     \
                     num_items, nq, nkv, page_size, ps, max_blocks, num_pages, window, scale_log2, num_splits,     \

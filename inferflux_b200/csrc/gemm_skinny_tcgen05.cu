@@ -26,50 +26,19 @@
 // No TMA multicast is used.  Every wait on an mbarrier is bounded: a wait that
 // runs out sets *error_flag and the block winds down (drains its copies, frees its
 // TMEM) instead of spinning.
-#include <cuda.h>
-
 #include <mutex>
 #include <unordered_map>
 
 #include "common.cuh"
+#include "ptx_sm100.cuh"
 
 namespace ifx {
 
 constexpr int kTileN = 128;       // weight rows per block (MMA M)
 constexpr int kTileK = 64;        // bf16 elements per k-block = one 128-byte swizzle row
-constexpr int kWaitLimit = 1 << 22;
 
 enum { MODE_STORE = 0, MODE_PARTIAL = 1, MODE_SWIGLU = 2 };
 
-__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-// Bounded wait for the phase with the given parity.  False if it never came.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-  for (int i = 0; i < kWaitLimit; ++i) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    if (ok) return true;
-  }
-  return false;
-}
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-      ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y)
-      : "memory");
-}
 __device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr) {
   // K-major tile of 128-byte rows, 128-byte swizzle: 8-row groups 1024 bytes apart.
   return (uint64_t)((addr & 0x3FFFFu) >> 4) | (1ull << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) |
@@ -244,38 +213,6 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
 
 // ------------------------------------------------------------------ host side
 
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  static std::once_flag once;
-  std::call_once(once, [] {
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-        q == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeTiledFn>(p);
-  });
-  return fn;
-}
-
-// A [rows, cols] row-major bfloat16 matrix, read in boxes of [box_rows, 64] with the 128-byte swizzle.
-static int make_map(CUtensorMap* map, const void* base, int rows, int cols, int box_rows) {
-  EncodeTiledFn fn = encode_fn();
-  if (!fn) return IFX_E_BADARG;
-  if ((reinterpret_cast<uintptr_t>(base) & 15) || (cols % 8)) return IFX_E_ALIGN;
-  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
-  cuuint32_t box[2] = {(cuuint32_t)kTileK, (cuuint32_t)box_rows};
-  cuuint32_t estr[2] = {1, 1};
-  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? 0 : 2000 + (int)r;
-}
-
 struct MapKey {
   const void* base;
   int rows, cols, box;
@@ -296,7 +233,7 @@ static int weight_map(CUtensorMap* out, const void* base, int rows, int cols) {
   auto it = cache.find(key);
   if (it == cache.end()) {
     CUtensorMap m;
-    int rc = make_map(&m, base, rows, cols, kTileN);
+    int rc = make_tensor_map_bf16(&m, base, rows, cols, kTileN);
     if (rc) return rc;
     it = cache.emplace(key, m).first;
   }
@@ -358,7 +295,7 @@ extern "C" int ifx_gemm_skinny(const void* act, const void* W, const float* bias
   int rc = weight_map(&mw, W, w_rows, K);
   if (rc) return rc;
   const int npad = M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128));
-  rc = make_map(&ma, act, M, K, npad);
+  rc = make_tensor_map_bf16(&ma, act, M, K, npad);
   if (rc) return rc;
 #define LAUNCH(NP, MD) \
   return launch_skinny<NP, MD>(mw, ma, bias, out, partials, M, N, K, splits, up_row_offset, out_is_f32, error_flag, stream)

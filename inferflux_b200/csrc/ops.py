@@ -327,7 +327,7 @@ class CudaKernels:
             splits = self.decode_splits(n, nkv, max_keys)
             _check(self.lib.ifx_attention_decode_bf16(
                 _ptr(q), _ptr(kv), _ptr(table), _ptr(ctx.decode_meta), _ptr(out), n, nq, nkv, d, *common, splits,
-                max_keys, _stream()), "attention (decoded tokens)")
+                max_keys, _ptr(self.error_flag), _stream()), "attention (decoded tokens)")
             self.launches += 1
         return out
 

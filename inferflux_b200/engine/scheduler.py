@@ -42,7 +42,7 @@ class SchedulerConfig:
             raise ValueError("mixed_prefill_budget_ratio must be in (0, 1]")
 
 
-@dataclass
+@dataclass(eq=False)
 class Request:
     request_id: Hashable
     prompt: List[int]
@@ -66,6 +66,16 @@ class Request:
     def remaining(self) -> int:
         return len(self.prompt) + len(self.output) - self.computed
 
+    def token_slice(self, start: int, count: int) -> List[int]:
+        """Tokens [start, start + count) of prompt + output, without joining the two lists."""
+        n = len(self.prompt)
+        end = start + count
+        if end <= n:
+            return self.prompt[start:end]
+        if start >= n:
+            return self.output[start - n:end - n]
+        return self.prompt[start:] + self.output[:end - n]
+
 
 @dataclass
 class ScheduledEntry:
@@ -84,7 +94,7 @@ class StepPlan:
     def step_entries(self) -> List[StepEntry]:
         out = []
         for e in self.entries:
-            toks = e.request.tokens[e.start:e.start + e.count]
+            toks = e.request.token_slice(e.start, e.count)
             out.append(StepEntry(e.request.request_id, toks, [e.count - 1] if e.wants_logits else []))
         return out
 
@@ -180,7 +190,7 @@ class Scheduler:
             ok = True
             # 1. decoding requests: one token each, oldest admission first
             decoding = [r for r in self.running if r.remaining == 1 and r.output]
-            prefilling = [r for r in self.running if r not in decoding]
+            prefilling = [r for r in self.running if not (r.remaining == 1 and r.output)]
             for r in decoding:
                 need = self._pages_for(r, r.computed + 1)
                 if budget < 1 or not self._fits(need, taken):
@@ -205,8 +215,8 @@ class Scheduler:
                 plan.entries.append(ScheduledEntry(r, r.computed, n, n == r.remaining))
                 prefill_budget -= n
             # 3. admissions, first come first served
-            while self.waiting and len(self.running) < cfg.max_batch_size and self.cache.num_free_slots > \
-                    sum(1 for e in plan.entries if e.request.request_id not in self.cache):
+            new_slots = 0
+            while self.waiting and len(self.running) < cfg.max_batch_size and self.cache.num_free_slots > new_slots:
                 r = self.waiting[0]
                 why = self._never_fits(r)
                 if why:
@@ -220,6 +230,7 @@ class Scheduler:
                 if n <= 0:
                     break
                 self.waiting.popleft()
+                new_slots += 1
                 r.status = "running"
                 r.admitted_at = self._admissions
                 self._admissions += 1
