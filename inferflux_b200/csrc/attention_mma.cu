@@ -550,6 +550,12 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap pool_map, const bf16*
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int item = blockIdx.x, g = blockIdx.y, split = blockIdx.z, num_splits = gridDim.z;
   const int G = nq / nkv;
+  pdl_launch_dependents();
+  if (tid == 0) {
+    for (int i = 0; i < 4 * STAGES; ++i) mbar_init(smem_addr(bars + i), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  pdl_wait();                                           // the queries, the cache and the tables are the step's own
   const int4 meta = decode_meta[item];
   const int t = meta.x;
   const int pos = meta.y;
@@ -570,10 +576,6 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap pool_map, const bf16*
       table = tbl_s;
       blk_base = b0;
     }
-  }
-  if (tid == 0) {
-    for (int i = 0; i < 4 * STAGES; ++i) mbar_init(smem_addr(bars + i), 1);
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   for (int i = tid; i < 16 * CPR; i += 128) {
     const int row = i / CPR, c = i % CPR;
@@ -820,23 +822,9 @@ int launch_decode_tma(const CUtensorMap& pool_map, const bf16* q, const int* blo
     if (e != cudaSuccess) return (int)e;
     configured = smem;
   }
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(num_items, nkv, num_splits);
-  cfg.blockDim = dim3(128);
-  cfg.dynamicSmemBytes = smem;
-  cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = 1;
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = num_splits;
-  cfg.attrs = attr;
-  cfg.numAttrs = num_splits > 1 ? 1 : 0;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, attn_decode_tma_kernel<D, STAGES>, pool_map, q, block_table, decode_meta,
-                                     out, nq, nkv, page_size, page_shift, max_blocks, num_pages, window, scale_log2,
-                                     tbl_cap, error_flag);
-  if (e != cudaSuccess) return (int)e;
-  return 0;
+  return launch_pdl(attn_decode_tma_kernel<D, STAGES>, dim3(num_items, nkv, num_splits), dim3(128), (size_t)smem, stream,
+                    num_splits, pool_map, q, block_table, decode_meta, out, nq, nkv, page_size, page_shift, max_blocks,
+                    num_pages, window, scale_log2, tbl_cap, error_flag);
 }
 
 // Tensor maps of cache pools (one per layer's pool), made once and kept.

@@ -5,6 +5,8 @@
 
 namespace ifx {
 
+int g_pdl_enabled = 1;
+
 // ------------------------------------------------------------------ embedding
 // out[t, :] = table[token[t], :] widened to float32.  A token id outside the
 // table (the host refuses those before launch) gives a row of zeros, never a read
@@ -74,6 +76,8 @@ reduce_add_rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ part,
                           float* __restrict__ sumsq, int* __restrict__ tickets, int chunks) {
   __shared__ float scratch[32];
   __shared__ int is_last;
+  pdl_launch_dependents();
+  pdl_wait();
   const int row = blockIdx.x, chunk = blockIdx.y;
   float* xr = x + (size_t)row * hidden;
   const float* pr = part + (size_t)row * hidden;
@@ -243,6 +247,12 @@ using namespace ifx;
 
 extern "C" {
 
+// 1 (default): kernels of the decode chain overlap their start with the previous kernel's end.
+int ifx_set_pdl(int enabled) {
+  g_pdl_enabled = enabled ? 1 : 0;
+  return 0;
+}
+
 int ifx_embed(const void* table, const int* tokens, float* out, int num_tokens, int hidden, int vocab,
               int dtype, cudaStream_t stream) {
   if (num_tokens <= 0) return 0;
@@ -297,15 +307,12 @@ int ifx_reduce_add_rmsnorm(float* x, const float* part, const float* w, void* ou
   dim3 grid(rows, chunks);
   const size_t stride = (size_t)rows * hidden;
   if (dtype == IFX_DT_F32)
-    reduce_add_rmsnorm_kernel<float><<<grid, 128, 0, stream>>>(x, part, w, (float*)out, hidden, eps, num_splits, stride,
-                                                               sumsq, tickets, chunks);
-  else if (dtype == IFX_DT_BF16)
-    reduce_add_rmsnorm_kernel<__nv_bfloat16><<<grid, 128, 0, stream>>>(x, part, w, (__nv_bfloat16*)out, hidden, eps,
-                                                                       num_splits, stride, sumsq, tickets, chunks);
-  else
-    return IFX_E_DTYPE;
-  IFX_CHECK_LAUNCH();
-  return 0;
+    return launch_pdl(reduce_add_rmsnorm_kernel<float>, grid, dim3(128), 0, stream, 1, x, part, w, (float*)out, hidden,
+                      eps, num_splits, stride, sumsq, tickets, chunks);
+  if (dtype == IFX_DT_BF16)
+    return launch_pdl(reduce_add_rmsnorm_kernel<__nv_bfloat16>, grid, dim3(128), 0, stream, 1, x, part, w,
+                      (__nv_bfloat16*)out, hidden, eps, num_splits, stride, sumsq, tickets, chunks);
+  return IFX_E_DTYPE;
 }
 
 int ifx_residual_add_partial(float* x, const float* part, int rows, int hidden, int num_splits, cudaStream_t stream) {

@@ -91,6 +91,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
 
   const uint32_t full0 = smem_addr(bars), empty0 = smem_addr(bars + stages), done_bar = smem_addr(bars + 2 * stages);
 
+  pdl_launch_dependents();
   if (threadIdx.x == 0) {
     for (int s = 0; s < stages; ++s) {
       mbar_init(full0 + 8 * s, 1);
@@ -115,7 +116,23 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     if (lane == 0) {
       int issued = 0;
       bool ok = true;
-      for (int i = 0; i < num_kb && ok; ++i) {
+      // The weights do not depend on the kernel before this one: the first ring of weight tiles is
+      // on its way before the activations are known to be ready.
+      const int early = min(stages, num_kb);
+      for (int i = 0; i < early; ++i) {
+        const uint32_t dst = smem_addr(smem + (size_t)i * STAGE_BYTES);
+        const uint32_t bar = full0 + 8 * i;
+        mbar_expect_tx(bar, STAGE_BYTES);
+        const int kx = (kb0 + i) * kTileK;
+        tma_load_2d(dst, &map_w, kx, n0, bar);
+        if (MODE == MODE_SWIGLU) tma_load_2d(dst + W_BYTES, &map_w, kx, up_row_offset + n0, bar);
+      }
+      pdl_wait();
+      for (int i = 0; i < early; ++i)
+        tma_load_2d(smem_addr(smem + (size_t)i * STAGE_BYTES) + W_TILES * W_BYTES, &map_a, (kb0 + i) * kTileK, 0,
+                    full0 + 8 * i);
+      issued = early;
+      for (int i = early; i < num_kb && ok; ++i) {
         const int s = i % stages;
         ok = mbar_wait(empty0 + 8 * s, ((i / stages) & 1) ^ 1);
         if (!ok) break;
@@ -165,6 +182,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     // ----------------------------------------------------------- epilogue
     const int quarter = warp & 3;                 // TMEM lanes this warp may read
     const int n = n0 + quarter * 32 + lane;
+    pdl_wait();                                   // nothing is written before the kernel in front has finished
     bool ok = mbar_wait(done_bar, 0);
     if (!ok && lane == 0) atomicExch(error_flag, 3);
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -266,10 +284,8 @@ static int launch_skinny(const CUtensorMap& mw, const CUtensorMap& ma, const flo
     configured = smem;
   }
   dim3 grid((N + kTileN - 1) / kTileN, splits);
-  gemm_skinny_kernel<NPAD, MODE><<<grid, 192, smem, stream>>>(mw, ma, bias, out, partials, M, N, K, per_split,
-                                                              up_row_offset, out_is_f32, stages, error_flag);
-  IFX_CHECK_LAUNCH();
-  return 0;
+  return launch_pdl(gemm_skinny_kernel<NPAD, MODE>, grid, dim3(192), smem, stream, 1, mw, ma, bias, out, partials, M, N,
+                    K, per_split, up_row_offset, out_is_f32, stages, error_flag);
 }
 
 }  // namespace ifx

@@ -9,6 +9,7 @@ Tensors are passed as raw device pointers on torch's current stream.
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Optional
 
 import torch
@@ -86,6 +87,8 @@ class CudaKernels:
             getattr(self.lib, fn).restype = ctypes.c_int
         with torch.cuda.device(self.device):
             _check(self.lib.ifx_cublas_init(), "cublas init")
+        if os.environ.get("INFERFLUX_B200_PDL", "1") == "0":      # for measurements: no overlap of consecutive kernels
+            self.lib.ifx_set_pdl(0)
         self.launches = 0            # kernels of this library launched so far
         self.library_calls = 0       # cuBLAS products called so far
         # scratch of the many-block reduce + norm: sums of squares per (row, chunk), a ticket per row

@@ -23,6 +23,8 @@ __global__ void rope_append_kernel(const T* __restrict__ qkv, const float* __res
                                    const int* __restrict__ req_slot, const int* __restrict__ block_table,
                                    int max_blocks, int page_size, int num_pages, T* __restrict__ kv_pool,
                                    T* __restrict__ q_out, int nq, int nkv, int d, int write_cache) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int t = blockIdx.x;
   const int head = blockIdx.y;                      // [0, nq) q, [nq, nq+nkv) k, then v
   const int width = (nq + 2 * nkv) * d;
@@ -103,16 +105,14 @@ extern "C" int ifx_rope_append(const void* qkv, const float* qkv_partial, int nu
   dim3 grid(num_tokens, nq + 2 * nkv);
   int threads = d / 2 >= 64 ? 64 : 32;
   if (dtype == IFX_DT_F32)
-    rope_append_kernel<float><<<grid, threads, 0, stream>>>(
-        (const float*)qkv, qkv_partial, num_splits, split_stride, bias, inv_freq, rot, interleaved, positions, token_req, req_slot, block_table,
-        max_blocks, page_size, num_pages, (float*)kv_pool, (float*)q_out, nq, nkv, d, write_cache);
-  else if (dtype == IFX_DT_BF16)
-    rope_append_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>(
-        (const __nv_bfloat16*)qkv, qkv_partial, num_splits, split_stride, bias, inv_freq, rot, interleaved, positions, token_req, req_slot,
-        block_table, max_blocks, page_size, num_pages, (__nv_bfloat16*)kv_pool, (__nv_bfloat16*)q_out, nq,
-        nkv, d, write_cache);
-  else
-    return IFX_E_DTYPE;
-  IFX_CHECK_LAUNCH();
-  return 0;
+    return launch_pdl(rope_append_kernel<float>, grid, dim3(threads), 0, stream, 1, (const float*)qkv, qkv_partial,
+                      num_splits, split_stride, bias, inv_freq, rot, interleaved, positions, token_req, req_slot,
+                      block_table, max_blocks, page_size, num_pages, (float*)kv_pool, (float*)q_out, nq, nkv, d,
+                      write_cache);
+  if (dtype == IFX_DT_BF16)
+    return launch_pdl(rope_append_kernel<__nv_bfloat16>, grid, dim3(threads), 0, stream, 1,
+                      (const __nv_bfloat16*)qkv, qkv_partial, num_splits, split_stride, bias, inv_freq, rot,
+                      interleaved, positions, token_req, req_slot, block_table, max_blocks, page_size, num_pages,
+                      (__nv_bfloat16*)kv_pool, (__nv_bfloat16*)q_out, nq, nkv, d, write_cache);
+  return IFX_E_DTYPE;
 }
