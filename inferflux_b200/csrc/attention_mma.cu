@@ -521,7 +521,9 @@ attn_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kv_pool,
 // warp's lane 0 fetches it with cp.async.bulk.tensor boxes [16 keys x 64 elements]
 // (128-byte swizzle) from the pool seen as a matrix [pages * 2 * nkv * page_size, D],
 // and the warp waits on the stage's mbarrier.  No per-lane address arithmetic, no
-// padding: ldmatrix reads the swizzled tiles without bank conflicts.
+// padding: ldmatrix reads the swizzled tiles without bank conflicts.  Keys of a tile
+// beyond the token's range get zero weight; what the page holds there is finite (the
+// pool starts as zeros and only finite values are ever written to it).
 template <int D, int STAGES>
 __global__ void __launch_bounds__(128)
 attn_decode_tma_kernel(const __grid_constant__ CUtensorMap pool_map, const bf16* __restrict__ q,
@@ -636,14 +638,6 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap pool_map, const bf16*
     ok = mbar_wait(my_bar0 + 8 * stage, (n_iter / STAGES) & 1);
     if (!ok) break;
     const uint32_t kt = my_stage0 + stage * STAGE_BYTES, vt = kt + TILE_BYTES;
-    if (base + 16 > k1) {                                 // the range ends inside this tile: what lies behind it in
-      const int valid = k1 - base;                        // the page is someone's old data; never multiply by it
-      for (int i = lane; i < (16 - valid) * (D / 8); i += 32) {
-        const int row = valid + i / (D / 8), c = (i % (D / 8)) * 8;
-        asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(vt + tile_off(row, c)), "r"(0) : "memory");
-      }
-      __syncwarp();
-    }
     float s[2][4];
 #pragma unroll
     for (int i = 0; i < 2; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.0f;
@@ -948,7 +942,7 @@ int ifx_attention_mma_supports(int d) {
 // max_keys: no request of the step holds more keys than this (sizes the shared-memory copy of the block table).
 int ifx_attention_prefill_bf16(const void* q, const void* kv_pool, const int* block_table, const int* tiles,
                                const int* req_slot, void* out, int num_tiles, int nq, int nkv, int d, int page_size,
-                               int max_blocks, int num_pages, int window, float scale, int max_keys,
+                               int max_blocks, int num_pages, int window, float scale, int max_keys, int* error_flag,
                                cudaStream_t stream) {
   if (num_tiles <= 0) return 0;
   if (nq <= 0 || nkv <= 0 || nq % nkv || page_size <= 0 || max_blocks <= 0 || nq > 65535) return IFX_E_BADARG;

@@ -318,7 +318,7 @@ class CudaKernels:
         if ctx.num_prefill_tiles:
             _check(self.lib.ifx_attention_prefill_bf16(
                 _ptr(q), _ptr(kv), _ptr(table), _ptr(ctx.prefill_tiles), _ptr(ctx.req_slot), _ptr(out),
-                ctx.num_prefill_tiles, nq, nkv, d, *common, int(ctx.max_kv_len), _stream()),
+                ctx.num_prefill_tiles, nq, nkv, d, *common, int(ctx.max_kv_len), _ptr(self.error_flag), _stream()),
                 "attention (prompt portions)")
             self.launches += 1
         n = ctx.num_decode_rows

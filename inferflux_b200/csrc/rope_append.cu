@@ -80,8 +80,91 @@ __global__ void rope_append_kernel(const T* __restrict__ qkv, const float* __res
       a = ra;
       c = rc;
     }
+    if (head >= nq) {                 // the cache only ever holds finite values: a masked key's value gets the
+      a = isfinite(a) ? a : 0.0f;     // weight zero, and zero times it must be zero whoever wrote it
+      c = isfinite(c) ? c : 0.0f;
+    }
     dst[e0] = from_f32<T>(a);
     dst[e1] = from_f32<T>(c);
+  }
+}
+
+// The same work for many tokens (prompt portions): one block per token.  The cosines
+// and sines of a token's angles are the same for all its heads, so they are computed
+// once into shared memory; then every thread moves 8 + 8 elements (a 16-byte chunk and
+// its rotation partner half a head away) per step.  Takes the common case only:
+// bfloat16 activations (not partial sums), whole-head split-half rotation, head
+// sizes that are multiples of 16.
+__global__ void __launch_bounds__(256)
+rope_append_rows_kernel(const __nv_bfloat16* __restrict__ qkv, const float* __restrict__ bias,
+                        const float* __restrict__ inv_freq, const int* __restrict__ positions,
+                        const int* __restrict__ token_req, const int* __restrict__ req_slot,
+                        const int* __restrict__ block_table, int max_blocks, int page_size, int num_pages,
+                        __nv_bfloat16* __restrict__ kv_pool, __nv_bfloat16* __restrict__ q_out, int nq, int nkv, int d,
+                        int write_cache) {
+  __shared__ float cs[128], sn[128];                    // d / 2 <= 128
+  const int t = blockIdx.x;
+  const int pos = positions[t];
+  const int half = d / 2;
+  for (int j = threadIdx.x; j < half; j += blockDim.x) sincosf((float)pos * inv_freq[j], &sn[j], &cs[j]);
+  size_t page_base = 0;
+  bool page_ok = false;
+  if (write_cache) {
+    const int slot = req_slot[token_req[t]];
+    const int page = block_table[(size_t)slot * max_blocks + pos / page_size];
+    page_ok = page >= 0 && page < num_pages;
+    page_base = (size_t)page * 2 * nkv * page_size * d + (size_t)(pos % page_size) * d;
+  }
+  __syncthreads();
+  const int width = (nq + 2 * nkv) * d;
+  const int cph = half / 8;                             // 16-byte chunks per half head
+  const int items = (nq + 2 * nkv) * cph;
+  const __nv_bfloat16* row = qkv + (size_t)t * width;
+  for (int it = threadIdx.x; it < items; it += blockDim.x) {
+    const int head = it / cph, c = (it % cph) * 8;
+    const bool is_q = head < nq, is_v = head >= nq + nkv;
+    __nv_bfloat16* dst;
+    if (is_q) {
+      dst = q_out + (size_t)t * nq * d + (size_t)head * d;
+    } else {
+      if (!write_cache || !page_ok) continue;
+      const int g = head - nq - (is_v ? nkv : 0);
+      dst = kv_pool + page_base + ((size_t)(is_v ? nkv : 0) + g) * page_size * d;
+    }
+    const uint4 lo_raw = *reinterpret_cast<const uint4*>(row + head * d + c);
+    const uint4 hi_raw = *reinterpret_cast<const uint4*>(row + head * d + half + c);
+    const __nv_bfloat162* lo2 = reinterpret_cast<const __nv_bfloat162*>(&lo_raw);
+    const __nv_bfloat162* hi2 = reinterpret_cast<const __nv_bfloat162*>(&hi_raw);
+    uint4 lo_out, hi_out;
+    __nv_bfloat162* lo_o = reinterpret_cast<__nv_bfloat162*>(&lo_out);
+    __nv_bfloat162* hi_o = reinterpret_cast<__nv_bfloat162*>(&hi_out);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      float2 a = __bfloat1622float2(lo2[k]), b = __bfloat1622float2(hi2[k]);
+      if (bias) {
+        a.x += bias[head * d + c + 2 * k];
+        a.y += bias[head * d + c + 2 * k + 1];
+        b.x += bias[head * d + half + c + 2 * k];
+        b.y += bias[head * d + half + c + 2 * k + 1];
+      }
+      if (!is_v) {
+        const float c0 = cs[c + 2 * k], s0 = sn[c + 2 * k], c1 = cs[c + 2 * k + 1], s1 = sn[c + 2 * k + 1];
+        const float ax = a.x * c0 - b.x * s0, bx = a.x * s0 + b.x * c0;
+        const float ay = a.y * c1 - b.y * s1, by = a.y * s1 + b.y * c1;
+        a = make_float2(ax, ay);
+        b = make_float2(bx, by);
+      }
+      if (!is_q) {                    // the cache only ever holds finite values
+        a.x = isfinite(a.x) ? a.x : 0.0f;
+        a.y = isfinite(a.y) ? a.y : 0.0f;
+        b.x = isfinite(b.x) ? b.x : 0.0f;
+        b.y = isfinite(b.y) ? b.y : 0.0f;
+      }
+      lo_o[k] = __floats2bfloat162_rn(a.x, a.y);
+      hi_o[k] = __floats2bfloat162_rn(b.x, b.y);
+    }
+    *reinterpret_cast<uint4*>(dst + c) = lo_out;
+    *reinterpret_cast<uint4*>(dst + half + c) = hi_out;
   }
 }
 
@@ -102,6 +185,15 @@ extern "C" int ifx_rope_append(const void* qkv, const float* qkv_partial, int nu
   if ((qkv == nullptr) == (qkv_partial == nullptr)) return IFX_E_BADARG;
   if (qkv_partial != nullptr && num_splits <= 0) return IFX_E_BADARG;
   const size_t split_stride = (size_t)num_tokens * (nq + 2 * nkv) * d;
+  if (dtype == IFX_DT_BF16 && qkv != nullptr && num_tokens >= 64 && rot == d && !interleaved && d % 16 == 0 &&
+      d <= 256 && (reinterpret_cast<uintptr_t>(qkv) % 16 == 0) && (reinterpret_cast<uintptr_t>(q_out) % 16 == 0) &&
+      (kv_pool == nullptr || reinterpret_cast<uintptr_t>(kv_pool) % 16 == 0)) {
+    rope_append_rows_kernel<<<num_tokens, 256, 0, stream>>>(
+        (const __nv_bfloat16*)qkv, bias, inv_freq, positions, token_req, req_slot, block_table, max_blocks, page_size,
+        num_pages, (__nv_bfloat16*)kv_pool, (__nv_bfloat16*)q_out, nq, nkv, d, write_cache);
+    IFX_CHECK_LAUNCH();
+    return 0;
+  }
   dim3 grid(num_tokens, nq + 2 * nkv);
   int threads = d / 2 >= 64 ? 64 : 32;
   if (dtype == IFX_DT_F32)

@@ -266,13 +266,16 @@ def test_attention_over_pages(cuda_kernels, dtype, nq, nkv, d, page, window):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("many", [False, True])
 @pytest.mark.parametrize("nq,nkv,d,rot,interleaved,bias", [
     (4, 2, 16, 16, False, True), (6, 2, 32, 32, False, False), (5, 1, 48, 24, True, True),
-    (28, 4, 128, 128, False, True), (3, 3, 80, 0, False, True)])
-def test_rope_append(cuda_kernels, dtype, nq, nkv, d, rot, interleaved, bias):
+    (28, 4, 128, 128, False, True), (3, 3, 80, 0, False, True), (2, 1, 256, 256, False, True)])
+def test_rope_append(cuda_kernels, dtype, nq, nkv, d, rot, interleaved, bias, many):
     from inferflux_b200.parts.base import RotaryTable
     page = 8
     lens, spans = [5, 300, 41, 17], [5, 1, 30, 2]
+    if many:
+        lens, spans = [70, 300, 41, 17], [70, 100, 30, 2]        # enough tokens for the one-block-per-token kernel
     ctx, cache, slots = make_cache_case(dtype, nkv, d, page, lens, spans, num_pages=60, seed=6)
     ref_cache_kv = cache.kv.clone()
     T = ctx.num_tokens
