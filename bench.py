@@ -177,6 +177,7 @@ def time_decode(engine, cfg, batch, steps, warmup, sampler_clock=None):
     d2h = (engine.stats.d2h_bytes - d2h0) / steps
 
     # ---- the step function alone, timed on the device
+    engine.drain()
     rids = [r.request_id for r in engine.scheduler.running]
     assert len(rids) == batch, f"{len(rids)} of {batch} requests are still decoding"
     g = torch.Generator().manual_seed(1)

@@ -241,6 +241,16 @@ __global__ void scatter_i32_kernel(int* __restrict__ table, const int* __restric
   if (at >= 0 && at < table_size) table[at] = value[i];
 }
 
+// dst[dst_index[i]] = src[src_index[i]]: tokens sampled by the previous step go straight into
+// this step's token ids without passing through the host.
+__global__ void relay_i32_kernel(int* __restrict__ dst, const int* __restrict__ dst_index, const int* __restrict__ src,
+                                 const int* __restrict__ src_index, int n, int dst_size, int src_size) {
+  int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const int d = dst_index[i], s = src_index[i];
+  if (d >= 0 && d < dst_size && s >= 0 && s < src_size) dst[d] = src[s];
+}
+
 }  // namespace ifx
 
 using namespace ifx;
@@ -378,6 +388,14 @@ int ifx_gather_rows(const float* x, const int* rows, float* out, int num_rows, i
                     cudaStream_t stream) {
   if (num_rows <= 0) return 0;
   gather_rows_kernel<<<num_rows, 256, 0, stream>>>(x, rows, out, hidden, num_src_rows);
+  IFX_CHECK_LAUNCH();
+  return 0;
+}
+
+int ifx_relay_i32(int* dst, const int* dst_index, const int* src, const int* src_index, int n, int dst_size,
+                  int src_size, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  relay_i32_kernel<<<(n + 127) / 128, 128, 0, stream>>>(dst, dst_index, src, src_index, n, dst_size, src_size);
   IFX_CHECK_LAUNCH();
   return 0;
 }

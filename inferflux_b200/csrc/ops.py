@@ -83,7 +83,7 @@ class CudaKernels:
                    "ifx_gemm_cublas_bf16", "ifx_cublas_init", "ifx_argmax", "ifx_penalties", "ifx_logit_bias",
                    "ifx_sample", "ifx_attention_mma_supports", "ifx_attention_prefill_bf16",
                    "ifx_attention_decode_bf16", "ifx_gemm_skinny", "ifx_residual_add_partial",
-                   "ifx_reduce_partial", "ifx_reduce_add_rmsnorm", "ifx_argmax_chunks"):
+                   "ifx_reduce_partial", "ifx_reduce_add_rmsnorm", "ifx_argmax_chunks", "ifx_relay_i32"):
             getattr(self.lib, fn).restype = ctypes.c_int
         with torch.cuda.device(self.device):
             _check(self.lib.ifx_cublas_init(), "cublas init")
@@ -181,6 +181,13 @@ class CudaKernels:
         if n:
             _check(self.lib.ifx_scatter_i32(_ptr(table), _ptr(index), _ptr(value), n, table.numel(), _stream()),
                    "scatter_i32")
+            self.launches += 1
+
+    def relay_i32(self, dst, dst_index, src, src_index):
+        n = dst_index.numel()
+        if n:
+            _check(self.lib.ifx_relay_i32(_ptr(dst), _ptr(dst_index), _ptr(src), _ptr(src_index), n, dst.numel(),
+                                          src.numel(), _stream()), "relay_i32")
             self.launches += 1
 
     # ------------------------------------------------------------------ linear

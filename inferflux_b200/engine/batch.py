@@ -59,7 +59,8 @@ class StepContext:
 
     @classmethod
     def build(cls, kernels, dtype, device, entries: Sequence[StepEntry], starts: Sequence[int],
-              slots: Sequence[int], table_updates: Sequence[Sequence[tuple]] = ()):
+              slots: Sequence[int], table_updates: Sequence[Sequence[tuple]] = (),
+              relay: Optional[Sequence[tuple]] = None):
         """Pack the arrays for `entries`; `starts[i]` is how many tokens request i
         already holds, `slots[i]` its slot, `table_updates[g]` the block-table
         entries of group g that changed since the last step."""
@@ -107,6 +108,9 @@ class StepContext:
         for g, ups in enumerate(table_updates):
             sections[f"upd_index_{g}"] = [u[0] for u in ups]
             sections[f"upd_page_{g}"] = [u[1] for u in ups]
+        # tokens that the previous step sampled and that are still on the device: (flat position here, row there)
+        sections["upd_relay_dst"] = [d for d, _s in (relay or ())]
+        sections["upd_relay_src"] = [s_ for _d, s_ in (relay or ())]
         offsets, flat = {}, []
         core_len = 0
         for name, vals in sections.items():
@@ -128,6 +132,8 @@ class StepContext:
         ctx.table_updates = [(dev[offsets[f"upd_index_{g}"][0]:][:offsets[f"upd_index_{g}"][1]],
                               dev[offsets[f"upd_page_{g}"][0]:][:offsets[f"upd_page_{g}"][1]])
                              for g in range(len(table_updates))]
+        ctx.relay_dst = dev[offsets["upd_relay_dst"][0]:][:offsets["upd_relay_dst"][1]]
+        ctx.relay_src = dev[offsets["upd_relay_src"][0]:][:offsets["upd_relay_src"][1]]
         return ctx
 
     _CORE = ("token_ids", "positions", "token_req", "cu_seqlens", "kv_lens", "req_slot", "logit_rows",

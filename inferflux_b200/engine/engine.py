@@ -23,7 +23,7 @@ import torch
 from ..models.loading import load_model, parse_dtype, random_model
 from ..sampling import Sampler, SamplingParams, SamplingRow
 from .runner import ModelRunner
-from .scheduler import Request, Scheduler, SchedulerConfig
+from .scheduler import PENDING, Request, Scheduler, SchedulerConfig, StepPlan
 
 
 @dataclass
@@ -37,6 +37,16 @@ class GenerationResult:
     @property
     def completion_tokens(self) -> int:
         return len(self.token_ids)
+
+
+@dataclass
+class _Inflight:
+    """A step that has been launched and whose sampled tokens have not been read yet."""
+    plan: StepPlan
+    ids: Optional[torch.Tensor]              # int32 on the device, one per entry that wanted logits
+    host: Optional[torch.Tensor]             # pinned copy under way (CUDA)
+    event: Optional[object]
+    row_of: dict                             # request id -> its row in `ids`
 
 
 @dataclass
@@ -55,7 +65,8 @@ class Engine:
                  kv_max_batch: int = 16, kv_max_seq: Optional[int] = None, kv_budget_mb: Optional[float] = None,
                  kv_budget_ratio: float = 0.20, max_batch_size: int = 32, max_batch_tokens: int = 16384,
                  chunked_prefill_tokens: int = 512, mixed_prefill_budget_ratio: float = 1.0,
-                 sampling_seed: int = 0, cuda_graphs: bool = True, loaded_model=None):
+                 sampling_seed: int = 0, cuda_graphs: bool = True, overlap_steps: bool = True,
+                 loaded_model=None):
         """`model`: a folder with config.json and model.safetensors.  Without it,
         `config` (a typed configuration) and `seed` make random weights on the device."""
         self.device = torch.device(device)
@@ -87,6 +98,11 @@ class Engine:
                                                    mixed_prefill_budget_ratio=mixed_prefill_budget_ratio),
                                    self.runner.cache, max_seq)
         self.sampler = Sampler(kernels, self.device)
+        # With overlap_steps a step is launched before the tokens of the one before are read: the
+        # scheduler, the packing of the batch and the launches run while the GPU works, and a token
+        # goes from one step's sampling to the next step's embedding on the device.
+        self.overlap_steps = bool(overlap_steps)
+        self._inflight: Optional[_Inflight] = None
         self._rng = random.Random(sampling_seed)
         self._next_id = 0
         self.stats = EngineStats()
@@ -130,35 +146,82 @@ class Engine:
         return request_id
 
     def has_unfinished(self) -> bool:
-        return self.scheduler.has_unfinished()
+        return self.scheduler.has_unfinished() or self._inflight is not None
 
     # -------------------------------------------------------------------- step
     def step(self) -> List[GenerationResult]:
-        """One scheduler decision, one model step, one sampling call.  Returns the
-        requests that finished in it (failed ones included)."""
-        plan = self.scheduler.schedule()
-        results = [self._result(r) for r in plan.failed]
-        if not plan.entries:
-            return results
-        entries = plan.step_entries()
-        logits = self.runner.step(entries)
-        rows = [SamplingRow(e.request.params, e.request.seed, len(e.request.output), e.request.output)
-                for e in plan.entries if e.wants_logits]
-        sampled: List[int] = []
-        if rows:
-            ids = self.sampler.sample(logits, rows)
-            sampled = ids.tolist()                          # the step's device-to-host read
-            self.stats.d2h_bytes += 4 * len(sampled)
-        self.stats.h2d_bytes += self.runner.last_ctx.meta_bytes
-        self.stats.steps += 1
+        """One scheduler decision, one model step, one sampling call.  Returns the requests
+        that finished (failed ones included).  With `overlap_steps` the tokens of a step are
+        read while the next step runs, so a request's finish is reported one step later."""
+        results: List[GenerationResult] = []
+        prev = self._inflight
+        overlap = self.overlap_steps and not any(r.params.has_penalties for r in self.scheduler.running)
+        if prev is not None and not overlap:
+            results += self._finalize(prev)
+            prev = self._inflight = None
+        plan = self.scheduler.schedule(inflight=prev is not None)
+        if plan.needs_drain:
+            results += self._finalize(prev)
+            prev = self._inflight = None
+            plan = self.scheduler.schedule()
+        results += [self._result(r) for r in plan.failed]
+        launched = None
+        if plan.entries:
+            entries = plan.step_entries()
+            relay, flat = [], 0
+            for e, se in zip(plan.entries, entries):
+                if se.tokens and se.tokens[-1] == PENDING:      # sampled by the step in flight, still on the device
+                    se.tokens = list(se.tokens[:-1]) + [0]
+                    relay.append((flat + len(se.tokens) - 1, prev.row_of[e.request.request_id]))
+                flat += len(se.tokens)
+            logits = self.runner.step(entries, relay=(relay, prev.ids) if relay else None)
+            rows = [SamplingRow(e.request.params, e.request.seed, len(e.request.output), e.request.output)
+                    for e in plan.entries if e.wants_logits]
+            ids = host = event = None
+            if rows:
+                ids = self.sampler.sample(logits, rows)
+                if ids.is_cuda:
+                    host = torch.empty(ids.shape, dtype=ids.dtype, pin_memory=True)
+                    host.copy_(ids, non_blocking=True)          # the step's device-to-host read
+                    event = torch.cuda.Event()
+                    event.record()
+                self.stats.d2h_bytes += 4 * len(rows)
+            self.scheduler.advance(plan)
+            wanting = [e.request.request_id for e in plan.entries if e.wants_logits]
+            launched = _Inflight(plan, ids, host, event, {rid: i for i, rid in enumerate(wanting)})
+            self.stats.h2d_bytes += self.runner.last_ctx.meta_bytes
+            self.stats.steps += 1
+            self.stats.prompt_tokens += sum(e.count for e in plan.entries if e.count > 1 or not e.request.output)
+            self.stats.generated_tokens += len(rows)
+        if prev is not None:
+            results += self._finalize(prev)
+        self._inflight = launched
+        if launched is not None and not overlap:
+            results += self._finalize(launched)
+            self._inflight = None
+        self.stats.preemptions = self.scheduler.num_preemptions
+        return results
+
+    def _finalize(self, step: _Inflight) -> List[GenerationResult]:
+        """Read a launched step's tokens and let the scheduler account for them."""
+        if step.ids is None:
+            sampled: List[int] = []
+        elif step.host is not None:
+            step.event.synchronize()
+            sampled = step.host.tolist()
+        else:
+            sampled = step.ids.tolist()
         if self.stats.steps % 32 == 1 and hasattr(self.kernels, "check_errors"):
             self.kernels.check_errors()                     # a kernel whose bounded wait ran out says so here
-        self.stats.prompt_tokens += sum(e.count for e in plan.entries if e.count > 1 or not e.request.output)
-        self.stats.generated_tokens += len(sampled)
-        self.stats.preemptions = self.scheduler.num_preemptions
-        for r in self.scheduler.update(plan, sampled):
-            results.append(self._result(r))
-        return results
+        return [self._result(r) for r in self.scheduler.resolve(step.plan, sampled)]
+
+    def drain(self) -> List[GenerationResult]:
+        """Read the tokens of the step in flight, if any."""
+        if self._inflight is None:
+            return []
+        out = self._finalize(self._inflight)
+        self._inflight = None
+        return out
 
     @staticmethod
     def _result(r: Request) -> GenerationResult:

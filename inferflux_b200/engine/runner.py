@@ -85,10 +85,12 @@ class ModelRunner:
                     raise StepError(f"request {e.request_id!r}: wanted place {w} is outside its "
                                     f"{len(e.tokens)} tokens")
 
-    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+    def step(self, entries: Sequence[StepEntry], relay=None) -> torch.Tensor:
         """Run only the tokens given, as one batch.  Returns float32 logits
         [number of wanted places, vocab] in the order of the entries and of `want`.
-        Raises OutOfPages (nothing taken, nothing run) when the pool cannot hold the step."""
+        Raises OutOfPages (nothing taken, nothing run) when the pool cannot hold the step.
+        `relay` = (pairs, ids): for each pair (flat position, row) the token at that position is
+        ids[row], an int32 device tensor the previous step's sampling left (the host has not read it)."""
         entries = list(entries)
         if not entries:
             return torch.empty((0, self.vocab_size), dtype=torch.float32, device=self.device)
@@ -120,9 +122,10 @@ class ModelRunner:
             slots.append(cache.slot(e.request_id))
 
         ctx = StepContext.build(self.kernels, self.dtype, self.device, entries, starts, slots,
-                                cache.drain_table_updates())
+                                cache.drain_table_updates(), relay[0] if relay else None)
         for group, (index, page) in zip(cache.groups, ctx.table_updates):
             self.kernels.scatter_i32(group.table, index, page)
+        ctx.relay_ids = relay[1] if relay else None
         logits = self._forward(ctx, entries)
         for e, start in zip(entries, starts):
             cache.commit(e.request_id, start + len(e.tokens))
@@ -132,8 +135,14 @@ class ModelRunner:
         return logits
 
     # ------------------------------------------------------------------ graphs
+    def _relay(self, ctx: StepContext) -> None:
+        """Put the tokens that are still on the device into the step's token ids."""
+        if ctx.relay_ids is not None and ctx.relay_dst.numel():
+            self.kernels.relay_i32(ctx.token_ids, ctx.relay_dst, ctx.relay_ids, ctx.relay_src)
+
     def _forward(self, ctx: StepContext, entries) -> torch.Tensor:
         if not self.cuda_graphs or ctx.max_span != 1 or ctx.num_logit_rows != ctx.num_tokens:
+            self._relay(ctx)
             return self.model.forward(ctx, self.cache)
         bucket = 256
         while bucket < ctx.max_kv_len:
@@ -144,12 +153,14 @@ class ModelRunner:
             if len(self._graphs) >= self.MAX_GRAPHS:
                 self._graphs.pop(next(iter(self._graphs)))
             self._graphs[key] = [1, None, None, None]
+            self._relay(ctx)
             return self.model.forward(ctx, self.cache)
         slot[0] += 1
         if slot[1] is None:                                # second time: capture
             static = torch.empty_like(ctx.core_buffer())
             static.copy_(ctx.core_buffer())
             ctx.rebind(static)
+            self._relay(ctx)
             ctx.max_kv_len = bucket                        # what depends on the context is fixed per bucket
             torch.cuda.synchronize(self.device)
             graph = torch.cuda.CUDAGraph()
@@ -160,6 +171,8 @@ class ModelRunner:
             slot.append(self.kernels.launches - launches)
         else:
             slot[2].copy_(ctx.core_buffer(), non_blocking=True)
+            ctx.rebind(slot[2])
+            self._relay(ctx)
             self.kernels.launches += slot[4]
         slot[1].replay()
         self.graph_replays += 1

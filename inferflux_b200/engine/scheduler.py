@@ -27,6 +27,8 @@ from typing import Deque, Dict, Hashable, List, Optional, Sequence
 from ..sampling.params import SamplingParams
 from .batch import StepEntry
 
+PENDING = -1        # stands in a request's output for a token that has been sampled on the device but not read yet
+
 
 @dataclass
 class SchedulerConfig:
@@ -57,6 +59,8 @@ class Request:
     finish_reason: Optional[str] = None
     preemptions: int = 0
     admitted_at: int = -1
+    pending: int = 0                  # PENDING entries at the end of `output`
+    discard: bool = False             # finished, but still part of the step in flight: that token is dropped
 
     @property
     def tokens(self) -> List[int]:
@@ -90,6 +94,7 @@ class StepPlan:
     entries: List[ScheduledEntry] = field(default_factory=list)
     preempted: List[Request] = field(default_factory=list)
     failed: List[Request] = field(default_factory=list)
+    needs_drain: bool = False         # a request would have to be preempted while tokens are pending
 
     def step_entries(self) -> List[StepEntry]:
         out = []
@@ -115,6 +120,7 @@ class Scheduler:
         self.waiting: Deque[Request] = deque()
         self.running: List[Request] = []
         self.finished: List[Request] = []
+        self.finishing: List[Request] = []       # finished, but the step in flight still holds their pages
         self._arrivals = 0
         self._admissions = 0
         self.num_preemptions = 0
@@ -133,7 +139,7 @@ class Scheduler:
         self.waiting.append(request)
 
     def has_unfinished(self) -> bool:
-        return bool(self.waiting or self.running)
+        return bool(self.waiting or self.running or self.finishing)
 
     # ------------------------------------------------------------------ helpers
     def _never_fits(self, r: Request) -> Optional[str]:
@@ -176,10 +182,21 @@ class Scheduler:
             self.cache.free(r.request_id)
         if r in self.running:
             self.running.remove(r)
+        if r in self.finishing:
+            self.finishing.remove(r)
         self.finished.append(r)
 
     # ---------------------------------------------------------------- schedule
-    def schedule(self) -> StepPlan:
+    def _may_continue(self, r: Request) -> bool:
+        """False while a request has to wait for its pending token: it may be the last one."""
+        if not r.pending:
+            return True
+        return len(r.output) < r.max_tokens and len(r.prompt) + len(r.output) < self.max_seq_len
+
+    def schedule(self, inflight: bool = False) -> StepPlan:
+        """Decide the next step.  With `inflight` the previous step's tokens are not known yet
+        (PENDING): requests go on with the pending token, which the step takes from the device;
+        if a preemption would be needed the plan only says `needs_drain` and changes nothing."""
         cfg = self.config
         plan = StepPlan()
         # Plans are made against the pages that are free now; `taken` counts what this plan has promised.
@@ -189,8 +206,8 @@ class Scheduler:
             budget = cfg.max_batch_tokens
             ok = True
             # 1. decoding requests: one token each, oldest admission first
-            decoding = [r for r in self.running if r.remaining == 1 and r.output]
-            prefilling = [r for r in self.running if not (r.remaining == 1 and r.output)]
+            decoding = [r for r in self.running if r.remaining == 1 and r.output and self._may_continue(r)]
+            prefilling = [r for r in self.running if not (r.remaining == 1 and r.output) and r.remaining > 0]
             for r in decoding:
                 need = self._pages_for(r, r.computed + 1)
                 if budget < 1 or not self._fits(need, taken):
@@ -200,6 +217,10 @@ class Scheduler:
                 plan.entries.append(ScheduledEntry(r, r.computed, 1, True))
                 budget -= 1
             if not ok:
+                if inflight:
+                    plan.entries = []
+                    plan.needs_drain = True
+                    return plan
                 victim = max(self.running, key=lambda r: r.admitted_at)
                 self._preempt(victim, plan)
                 continue
@@ -241,6 +262,9 @@ class Scheduler:
                 prefill_budget -= n
             if plan.entries or not self.running:
                 break
+            if inflight:                        # everyone may simply be waiting for pending tokens
+                plan.needs_drain = True
+                return plan
             # nothing can move although requests are live: free the newest one's pages
             victim = max(self.running, key=lambda r: r.admitted_at)
             self._preempt(victim, plan)
@@ -263,24 +287,55 @@ class Scheduler:
         return lo
 
     # ------------------------------------------------------------------- update
-    def update(self, plan: StepPlan, sampled: Sequence[int]) -> List[Request]:
-        """Account for a step that ran: `sampled` holds one token per entry that
-        wanted logits, in order.  Returns the requests that finished."""
-        done = []
-        it = iter(sampled)
+    def advance(self, plan: StepPlan) -> None:
+        """The step has been launched: its tokens count as stored, and every entry that
+        wanted logits has a token coming whose value is not known yet."""
         for e in plan.entries:
             r = e.request
             r.computed = e.start + e.count
+            if e.wants_logits:
+                r.output.append(PENDING)
+                r.pending += 1
+
+    def resolve(self, plan: StepPlan, sampled: Sequence[int]) -> List[Request]:
+        """The tokens of a launched step are known: `sampled` holds one per entry that
+        wanted logits, in order.  Returns the requests that are finished and freed."""
+        done = []
+        it = iter(sampled)
+        for e in plan.entries:
             if not e.wants_logits:
                 continue
+            r = e.request
             tok = int(next(it))
-            r.output.append(tok)
+            if r.discard:                                    # it had already finished when this step was launched
+                r.discard = False
+                self._finish(r, r.finish_reason)
+                done.append(r)
+                continue
+            idx = len(r.output) - r.pending
+            r.output[idx] = tok
+            r.pending -= 1
+            reason = None
             if tok in r.eos_token_ids:
-                self._finish(r, "stop")
-            elif len(r.output) >= r.max_tokens:
-                self._finish(r, "length")
-            elif len(r.prompt) + len(r.output) >= self.max_seq_len:
-                self._finish(r, "length")                      # no room for another position
-            if r.status == "finished":
+                reason = "stop"
+            elif idx + 1 >= r.max_tokens or len(r.prompt) + idx + 1 >= self.max_seq_len:
+                reason = "length"
+            if reason is None:
+                continue
+            del r.output[idx + 1:]
+            if r.pending:                                    # the step in flight still works on its pages
+                r.pending = 0
+                r.discard = True
+                r.finish_reason = reason
+                r.status = "finishing"
+                self.running.remove(r)
+                self.finishing.append(r)
+            else:
+                self._finish(r, reason)
                 done.append(r)
         return done
+
+    def update(self, plan: StepPlan, sampled: Sequence[int]) -> List[Request]:
+        """advance + resolve in one go, for a step whose tokens are read right away."""
+        self.advance(plan)
+        return self.resolve(plan, sampled)

@@ -48,6 +48,10 @@ class PlainKernels:
         if index.numel():
             table.view(-1)[index.long()] = value
 
+    def relay_i32(self, dst, dst_index, src, src_index):
+        if dst_index.numel():
+            dst[dst_index.long()] = src[src_index.long()]
+
     # ------------------------------------------------------------------ linear
     def linear(self, a, w, bias=None, out_dtype=None, allow_partial=False):
         y = a.to(self.acc) @ w.to(self.acc).t()

@@ -106,3 +106,35 @@ def test_no_extension_no_engine(monkeypatch, model_dirs):
     from inferflux_b200 import Engine
     with pytest.raises(BuildError):
         Engine(model_dirs["A"][0], dtype="float32")
+
+
+def test_overlapped_steps_give_the_same_tokens_on_the_gpu(model_dirs, tiny_configs):
+    """A step launched before the previous one's tokens are read takes them on the device;
+    the tokens generated are those of reading every step's tokens first."""
+    from inferflux_b200 import Engine, SamplingParams
+    cfg, page = tiny_configs["B"]
+    d, _ = model_dirs["B"]
+    prompts = [helpers.random_tokens(cfg.vocab_size, n, 700 + i) for i, n in enumerate([5, 21, 33, 2, 40, 11, 64, 17])]
+    params = [SamplingParams(temperature=0.0 if i % 2 == 0 else 0.8, seed=50 + i) for i in range(len(prompts))]
+    limits = [9, 40, 14, 1, 30, 3, 25, 33]
+
+    def run(overlap, pages):
+        eng = Engine(d, dtype="float32", kv_page_size=page, kv_num_pages=pages, kv_max_batch=8, kv_max_seq=96,
+                     chunked_prefill_tokens=16, max_batch_tokens=48, overlap_steps=overlap)
+        ids = [eng.add_request(p, sp, max_tokens=m) for p, sp, m in zip(prompts, params, limits)]
+        done = {}
+        while eng.has_unfinished():
+            for r in eng.step():
+                done[r.request_id] = r
+        assert not eng.runner.cache.live_requests()
+        return [(done[i].token_ids, done[i].finish_reason) for i in ids], eng
+    base, _ = run(False, 128)
+    over, eng = run(True, 128)
+    assert base == over and eng.runner.graph_replays > 0
+    tight, eng = run(True, 30)
+    assert base == tight and eng.stats.preemptions > 0
+    stop = base[1][0][7]
+    cut = base[1][0][:base[1][0].index(stop) + 1]
+    eng = Engine(d, dtype="float32", kv_page_size=page, kv_num_pages=128, kv_max_batch=8)
+    got = eng.generate([prompts[1]], params[1], max_tokens=40, eos_token_id=stop)[0]
+    assert got.token_ids == cut and got.finish_reason == "stop"

@@ -120,3 +120,45 @@ def test_temperature_sampling_is_reproducible_and_independent_of_the_batch(model
     # the sampler's own random numbers
     us = [philox_uniform(1234, 0, s) for s in range(2000)]
     assert 0.45 < float(np.mean(us)) < 0.55 and min(us) >= 0.0 and max(us) < 1.0 and len(set(us)) > 1990
+
+
+@pytest.mark.parametrize("pages", [64, 12])
+def test_overlapped_steps_give_the_same_tokens(pages, model_dirs, tiny_configs, loaded):
+    """Launching a step before the last one's tokens are read (they travel on the device)
+    changes nothing in what is generated: greedy and sampled, stopping on a token, on the
+    token limit and on the context limit, with and without preemption."""
+    from inferflux_b200 import Engine, SamplingParams
+    name = "A"
+    cfg, page = tiny_configs[name]
+    d, _ = model_dirs[name]
+    raw, W = loaded[name]
+    prompts = [helpers.random_tokens(cfg.vocab_size, n, 900 + i) for i, n in enumerate([5, 21, 33, 2, 40, 11])]
+    free_run = plain_qwen2.greedy_generate(raw, W, prompts[1], 12)
+    stop = free_run[5]
+    until_stop = free_run[:free_run.index(stop) + 1]
+    params = [SamplingParams(temperature=0.0), SamplingParams(temperature=0.0), SamplingParams(temperature=0.9, seed=4),
+              SamplingParams(temperature=0.0), SamplingParams(temperature=0.7, seed=9, top_k=20),
+              SamplingParams(temperature=0.0)]
+
+    def run(overlap):
+        eng = Engine(d, dtype="float32", device="cpu", kernels=PlainKernels(), kv_page_size=page, kv_num_pages=pages,
+                     kv_max_batch=4, kv_max_seq=48, chunked_prefill_tokens=16, max_batch_tokens=40, overlap_steps=overlap)
+        ids = [eng.add_request(p, sp, max_tokens=m, eos_token_id=stop) for p, sp, m in
+               zip(prompts, params, [9, 12, 14, 1, 30, 3])]
+        done = {}
+        while eng.has_unfinished():
+            for r in eng.step():
+                done[r.request_id] = r
+        assert eng.runner.cache.free_pages() == [pages] and not eng.runner.cache.live_requests()
+        return [(done[i].token_ids, done[i].finish_reason) for i in ids], eng.stats
+    a, sa = run(False)
+    b, sb = run(True)
+    assert a == b
+    assert a[1] == (until_stop, "stop") and a[3][1] == "length" and len(a[3][0]) == 1
+    assert a[4][1] == "length" and len(prompts[4]) + len(a[4][0]) == 48        # the context limit
+    assert all(PENDING not in toks for toks, _ in b)
+    if pages == 12:
+        assert sb.preemptions > 0
+
+
+PENDING = -1
