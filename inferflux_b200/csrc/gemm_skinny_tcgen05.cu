@@ -118,14 +118,15 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
       bool ok = true;
       // The weights do not depend on the kernel before this one: the first ring of weight tiles is
       // on its way before the activations are known to be ready.
+      const uint64_t stream_once = l2_evict_first_policy();
       const int early = min(stages, num_kb);
       for (int i = 0; i < early; ++i) {
         const uint32_t dst = smem_addr(smem + (size_t)i * STAGE_BYTES);
         const uint32_t bar = full0 + 8 * i;
         mbar_expect_tx(bar, STAGE_BYTES);
         const int kx = (kb0 + i) * kTileK;
-        tma_load_2d(dst, &map_w, kx, n0, bar);
-        if (MODE == MODE_SWIGLU) tma_load_2d(dst + W_BYTES, &map_w, kx, up_row_offset + n0, bar);
+        tma_load_2d_hint(dst, &map_w, kx, n0, bar, stream_once);
+        if (MODE == MODE_SWIGLU) tma_load_2d_hint(dst + W_BYTES, &map_w, kx, up_row_offset + n0, bar, stream_once);
       }
       pdl_wait();
       for (int i = 0; i < early; ++i)
@@ -140,8 +141,8 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         const uint32_t bar = full0 + 8 * s;
         mbar_expect_tx(bar, STAGE_BYTES);
         const int kx = (kb0 + i) * kTileK;
-        tma_load_2d(dst, &map_w, kx, n0, bar);
-        if (MODE == MODE_SWIGLU) tma_load_2d(dst + W_BYTES, &map_w, kx, up_row_offset + n0, bar);
+        tma_load_2d_hint(dst, &map_w, kx, n0, bar, stream_once);
+        if (MODE == MODE_SWIGLU) tma_load_2d_hint(dst + W_BYTES, &map_w, kx, up_row_offset + n0, bar, stream_once);
         tma_load_2d(dst + W_TILES * W_BYTES, &map_a, kx, 0, bar);
         issued = i + 1;
       }
