@@ -154,6 +154,85 @@ reduce_add_rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ part,
   }
 }
 
+// The norm without its row scale: x += delta (K-split partial sums, a tensor, or nothing),
+// pre = x * w rounded to T, and sumsq[row, chunk] = the chunk's sum of x^2.  The scale
+// rsqrt(sum(sumsq[row, :]) / hidden + eps) is a per-row scalar, so the matrix product that
+// consumes `pre` applies it to its accumulator instead (pre . W^T is linear in it): no block
+// has to wait for a row's other chunks, and the norm costs one pass over 512 columns a block.
+// MODE 0: no delta; 1: delta in T; 2: float32 partial sums [splits, rows, hidden].
+template <typename T, int MODE>
+__global__ void __launch_bounds__(128)
+prenorm_kernel(float* __restrict__ x, const void* __restrict__ delta_raw, const float* __restrict__ w,
+               T* __restrict__ pre, int hidden, int num_splits, size_t split_stride, float* __restrict__ sumsq,
+               int chunks) {
+  __shared__ float scratch[32];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int row = blockIdx.x, chunk = blockIdx.y;
+  float* xr = x + (size_t)row * hidden;
+  T* pr = pre + (size_t)row * hidden;
+  const int c0 = chunk * kNormChunk + threadIdx.x * 4;
+  float ss = 0.0f;
+  if (c0 + 3 < hidden && (hidden & 3) == 0) {
+    float4 v = *reinterpret_cast<const float4*>(xr + c0);
+    const float4 wv = *reinterpret_cast<const float4*>(w + c0);
+    if (MODE == 1) {
+      const T* d = reinterpret_cast<const T*>(delta_raw) + (size_t)row * hidden + c0;
+      v.x += to_f32(d[0]); v.y += to_f32(d[1]); v.z += to_f32(d[2]); v.w += to_f32(d[3]);
+    } else if (MODE == 2) {
+      const float* p = reinterpret_cast<const float*>(delta_raw) + (size_t)row * hidden + c0;
+      float4 d = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int s0 = 0; s0 < num_splits; s0 += kNormBatch) {
+        float4 q[kNormBatch];
+#pragma unroll
+        for (int j = 0; j < kNormBatch; ++j)
+          q[j] = s0 + j < num_splits ? __ldcg(reinterpret_cast<const float4*>(p + (size_t)(s0 + j) * split_stride))
+                                     : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int j = 0; j < kNormBatch; ++j) {
+          d.x += q[j].x; d.y += q[j].y; d.z += q[j].z; d.w += q[j].w;
+        }
+      }
+      v.x += d.x; v.y += d.y; v.z += d.z; v.w += d.w;
+    }
+    if (MODE != 0) *reinterpret_cast<float4*>(xr + c0) = v;
+    pr[c0] = from_f32<T>(v.x * wv.x);
+    pr[c0 + 1] = from_f32<T>(v.y * wv.y);
+    pr[c0 + 2] = from_f32<T>(v.z * wv.z);
+    pr[c0 + 3] = from_f32<T>(v.w * wv.w);
+    ss = v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+  } else {
+    for (int c = c0; c < min(c0 + 4, hidden); ++c) {
+      float v = xr[c];
+      if (MODE == 1) {
+        v += to_f32(reinterpret_cast<const T*>(delta_raw)[(size_t)row * hidden + c]);
+      } else if (MODE == 2) {
+        const float* p = reinterpret_cast<const float*>(delta_raw) + (size_t)row * hidden + c;
+        float d = 0.0f;
+        for (int s = 0; s < num_splits; ++s) d += __ldcg(p + (size_t)s * split_stride);
+        v += d;
+      }
+      if (MODE != 0) xr[c] = v;
+      pr[c] = from_f32<T>(v * w[c]);
+      ss += v * v;
+    }
+  }
+  ss = block_sum(ss, scratch);
+  if (threadIdx.x == 0) sumsq[(size_t)row * chunks + chunk] = ss;
+}
+
+// out = pre * rsqrt(sum(sumsq[row, :]) / hidden + eps): the plain tensor of a pre-normed row.
+template <typename T>
+__global__ void scale_rows_kernel(const T* __restrict__ pre, const float* __restrict__ sumsq, T* __restrict__ out,
+                                  int hidden, int chunks, float eps) {
+  const int row = blockIdx.x;
+  float total = 0.0f;
+  for (int c = 0; c < chunks; ++c) total += sumsq[(size_t)row * chunks + c];
+  const float r = rsqrtf(total / (float)hidden + eps);
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x)
+    out[(size_t)row * hidden + i] = from_f32<T>(to_f32(pre[(size_t)row * hidden + i]) * r);
+}
+
 // ------------------------------------------------------------------- SiLU*up
 // in [rows, 2*inter] = gate | up;  out[r, i] = silu(gate) * up, silu(g) = g / (1 + exp(-g)).
 template <typename T>
@@ -323,6 +402,47 @@ int ifx_reduce_add_rmsnorm(float* x, const float* part, const float* w, void* ou
     return launch_pdl(reduce_add_rmsnorm_kernel<__nv_bfloat16>, grid, dim3(128), 0, stream, 1, x, part, w,
                       (__nv_bfloat16*)out, hidden, eps, num_splits, stride, sumsq, tickets, chunks);
   return IFX_E_DTYPE;
+}
+
+// sumsq: float32 [rows, ceil(hidden / 512)].  delta == nullptr: no add; num_splits > 0: float32 partial sums.
+int ifx_prenorm(float* x, const void* delta, const float* w, void* pre, float* sumsq, int rows, int hidden,
+                int num_splits, int dtype, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (hidden <= 0 || num_splits < 0 || sumsq == nullptr) return IFX_E_BADARG;
+  const int chunks = (hidden + kNormChunk - 1) / kNormChunk;
+  if (chunks > 65535) return IFX_E_TOOBIG;
+  dim3 grid(rows, chunks);
+  const size_t stride = (size_t)rows * hidden;
+#define IFX_PRE(T, MODE) \
+  return launch_pdl(prenorm_kernel<T, MODE>, grid, dim3(128), 0, stream, 1, x, delta, w, (T*)pre, hidden, num_splits, \
+                    stride, sumsq, chunks)
+  if (dtype == IFX_DT_F32) {
+    if (!delta) IFX_PRE(float, 0);
+    if (num_splits > 0) IFX_PRE(float, 2);
+    IFX_PRE(float, 1);
+  }
+  if (dtype == IFX_DT_BF16) {
+    if (!delta) IFX_PRE(__nv_bfloat16, 0);
+    if (num_splits > 0) IFX_PRE(__nv_bfloat16, 2);
+    IFX_PRE(__nv_bfloat16, 1);
+  }
+#undef IFX_PRE
+  return IFX_E_DTYPE;
+}
+
+int ifx_scale_rows(const void* pre, const float* sumsq, void* out, int rows, int hidden, float eps, int dtype,
+                   cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  const int chunks = (hidden + kNormChunk - 1) / kNormChunk;
+  if (dtype == IFX_DT_F32)
+    scale_rows_kernel<float><<<rows, 256, 0, stream>>>((const float*)pre, sumsq, (float*)out, hidden, chunks, eps);
+  else if (dtype == IFX_DT_BF16)
+    scale_rows_kernel<__nv_bfloat16><<<rows, 256, 0, stream>>>((const __nv_bfloat16*)pre, sumsq, (__nv_bfloat16*)out,
+                                                               hidden, chunks, eps);
+  else
+    return IFX_E_DTYPE;
+  IFX_CHECK_LAUNCH();
+  return 0;
 }
 
 int ifx_residual_add_partial(float* x, const float* part, int rows, int hidden, int num_splits, cudaStream_t stream) {

@@ -69,7 +69,7 @@ __global__ void __launch_bounds__(192)
 gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a,
                    const float* __restrict__ bias, void* __restrict__ out, float* __restrict__ partials, int M, int N,
                    int K, int kblocks_per_split, int up_row_offset, int out_is_f32, int stages,
-                   int* __restrict__ error_flag) {
+                   const float* __restrict__ row_sumsq, int sumsq_chunks, float eps, int* __restrict__ error_flag) {
   constexpr int W_TILES = MODE == MODE_SWIGLU ? 2 : 1;
   constexpr uint32_t W_BYTES = kTileN * kTileK * 2;                 // 16 KB
   constexpr uint32_t A_BYTES = NPAD * kTileK * 2;
@@ -184,6 +184,18 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     const int quarter = warp & 3;                 // TMEM lanes this warp may read
     const int n = n0 + quarter * 32 + lane;
     pdl_wait();                                   // nothing is written before the kernel in front has finished
+    // Rows that arrive pre-normed (x * w without the norm's row scale) get the scale here:
+    // rsqrt(mean(x^2) + eps) from the per-chunk sums of squares the norm kernel left.
+    __shared__ float row_scale[128];
+    if (row_sumsq != nullptr) {
+      const int m = threadIdx.x - 64;             // the 128 epilogue threads, one token each
+      if (m < M) {
+        float total = 0.0f;
+        for (int c = 0; c < sumsq_chunks; ++c) total += __ldcg(&row_sumsq[(size_t)m * sumsq_chunks + c]);
+        row_scale[m] = rsqrtf(total / (float)K + eps);
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+    }
     bool ok = mbar_wait(done_bar, 0);
     if (!ok && lane == 0) atomicExch(error_flag, 3);
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -206,9 +218,10 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         for (int j = 0; j < 16; ++j) {
           const int m = c + j;
           if (m >= M) break;
-          float v = __uint_as_float(g[j]);
+          const float rs = row_sumsq != nullptr ? row_scale[m] : 1.0f;
+          float v = __uint_as_float(g[j]) * rs;
           if (MODE == MODE_SWIGLU) {
-            const float up = __uint_as_float(u[j]);
+            const float up = __uint_as_float(u[j]) * rs;
             v = v / (1.0f + expf(-v)) * up;
           }
           if (MODE == MODE_PARTIAL) {
@@ -267,8 +280,8 @@ static size_t skinny_smem_bytes(int npad, int mode, int stages) {
 
 template <int NPAD, int MODE>
 static int launch_skinny(const CUtensorMap& mw, const CUtensorMap& ma, const float* bias, void* out, float* partials,
-                         int M, int N, int K, int splits, int up_row_offset, int out_is_f32, int* error_flag,
-                         cudaStream_t stream) {
+                         int M, int N, int K, int splits, int up_row_offset, int out_is_f32, const float* row_sumsq,
+                         int sumsq_chunks, float eps, int* error_flag, cudaStream_t stream) {
   const int total_kblocks = (K + kTileK - 1) / kTileK;
   const int per_split = (total_kblocks + splits - 1) / splits;
   // as many stages as fit ~100 KB (two blocks per SM), at most the k-blocks of a split; SWIGLU blocks own their SM
@@ -286,7 +299,7 @@ static int launch_skinny(const CUtensorMap& mw, const CUtensorMap& ma, const flo
   }
   dim3 grid((N + kTileN - 1) / kTileN, splits);
   return launch_pdl(gemm_skinny_kernel<NPAD, MODE>, grid, dim3(192), smem, stream, 1, mw, ma, bias, out, partials, M, N,
-                    K, per_split, up_row_offset, out_is_f32, stages, error_flag);
+                    K, per_split, up_row_offset, out_is_f32, stages, row_sumsq, sumsq_chunks, eps, error_flag);
 }
 
 }  // namespace ifx
@@ -298,9 +311,12 @@ using namespace ifx;
 // mode 1: partials[splits, M, N] float32.
 // mode 2: W holds N gate rows at 0 and N up rows at up_row_offset; out[M, N] = silu(gate) * up, bfloat16.
 // error_flag: device int, set to non-zero if a bounded wait ran out (the output is then not valid).
+// row_sumsq (optional): float32 [M, sumsq_chunks]; the rows of `act` are then x * w of a norm over K
+// columns and every output row m is scaled by rsqrt(sum(row_sumsq[m, :]) / K + eps).
 extern "C" int ifx_gemm_skinny(const void* act, const void* W, const float* bias, void* out, float* partials, int M,
                                int N, int K, int w_rows, int splits, int mode, int up_row_offset, int out_is_f32,
-                               int* error_flag, cudaStream_t stream) {
+                               const float* row_sumsq, int sumsq_chunks, float eps, int* error_flag,
+                               cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if (K <= 0 || M > 128 || splits <= 0 || splits > 65535 || error_flag == nullptr) return IFX_E_BADARG;
   if (mode == MODE_STORE && splits != 1) return IFX_E_BADARG;
@@ -315,7 +331,8 @@ extern "C" int ifx_gemm_skinny(const void* act, const void* W, const float* bias
   rc = make_tensor_map_bf16(&ma, act, M, K, npad);
   if (rc) return rc;
 #define LAUNCH(NP, MD) \
-  return launch_skinny<NP, MD>(mw, ma, bias, out, partials, M, N, K, splits, up_row_offset, out_is_f32, error_flag, stream)
+  return launch_skinny<NP, MD>(mw, ma, bias, out, partials, M, N, K, splits, up_row_offset, out_is_f32, row_sumsq, \
+                               sumsq_chunks, eps, error_flag, stream)
 #define BY_NPAD(MD)                 \
   switch (npad) {                   \
     case 16: LAUNCH(16, MD);        \

@@ -26,6 +26,24 @@ class KernelError(RuntimeError):
     pass
 
 
+class ScaledRows:
+    """Rows of a norm without its row scale: `pre` = x * w in the run's dtype and `sumsq`
+    [rows, chunks] float32, the chunks' sums of x^2.  The true rows are
+    pre * rsqrt(sum(sumsq[row]) / hidden + eps); a matrix product that takes them applies that
+    per-row factor to its accumulator.  `CudaKernels.materialize_rows` gives the plain tensor."""
+
+    def __init__(self, pre: torch.Tensor, sumsq: torch.Tensor, eps: float):
+        self.pre, self.sumsq, self.eps = pre, sumsq, float(eps)
+
+    @property
+    def shape(self):
+        return self.pre.shape
+
+    @property
+    def dtype(self):
+        return self.pre.dtype
+
+
 class PartialSum:
     """The result of a matrix product whose K range was split over thread blocks:
     float32 partial sums [splits, rows, cols] that the consuming kernel adds, in split
@@ -83,7 +101,7 @@ class CudaKernels:
                    "ifx_gemm_cublas_bf16", "ifx_cublas_init", "ifx_argmax", "ifx_penalties", "ifx_logit_bias",
                    "ifx_sample", "ifx_attention_mma_supports", "ifx_attention_prefill_bf16",
                    "ifx_attention_decode_bf16", "ifx_gemm_skinny", "ifx_residual_add_partial",
-                   "ifx_reduce_partial", "ifx_reduce_add_rmsnorm", "ifx_argmax_chunks", "ifx_relay_i32"):
+                   "ifx_reduce_partial", "ifx_reduce_add_rmsnorm", "ifx_argmax_chunks", "ifx_relay_i32", "ifx_prenorm", "ifx_scale_rows"):
             getattr(self.lib, fn).restype = ctypes.c_int
         with torch.cuda.device(self.device):
             _check(self.lib.ifx_cublas_init(), "cublas init")
@@ -138,6 +156,37 @@ class CudaKernels:
             src, splits = delta, 0
         _check(self.lib.ifx_rmsnorm(_ptr(x), _ptr(src), _ptr(w), _ptr(out), T, H, ctypes.c_float(eps), splits,
                                     _DT[out_dtype], _stream()), "add_rmsnorm")
+        self.launches += 1
+        return out
+
+    def prenorm(self, x, delta, w, eps, out_dtype):
+        """The norm for a consumer that takes ScaledRows (x += delta first, as add_rmsnorm).
+        Few bfloat16 rows: one pass that leaves x * w and per-chunk sums of squares, the row scale
+        being applied by the matrix product that follows.  Otherwise the plain normed tensor."""
+        T, H = x.shape
+        if out_dtype != torch.bfloat16 or T > self.SKINNY_MAX_ROWS or H % 8:
+            return self.rmsnorm(x, w, eps, out_dtype) if delta is None else self.add_rmsnorm(x, delta, w, eps, out_dtype)
+        pre = torch.empty((T, H), dtype=out_dtype, device=x.device)
+        sumsq = torch.empty((T, -(-H // 512)), dtype=torch.float32, device=x.device)
+        if isinstance(delta, PartialSum):
+            _need(tuple(delta.shape) == (T, H), "prenorm: partial sums do not match x")
+            src, splits = delta.parts, delta.splits
+        else:
+            _need(delta is None or (delta.dtype == out_dtype and delta.shape == x.shape), "prenorm: delta must match x")
+            src, splits = delta, 0
+        _check(self.lib.ifx_prenorm(_ptr(x), _ptr(src), _ptr(w), _ptr(pre), _ptr(sumsq), T, H, splits, _DT[out_dtype],
+                                    _stream()), "prenorm")
+        self.launches += 1
+        return ScaledRows(pre, sumsq, eps)
+
+    def materialize_rows(self, h):
+        """A plain tensor from what `prenorm` returned."""
+        if not isinstance(h, ScaledRows):
+            return h
+        T, H = h.shape
+        out = torch.empty((T, H), dtype=h.dtype, device=h.pre.device)
+        _check(self.lib.ifx_scale_rows(_ptr(h.pre), _ptr(h.sumsq), _ptr(out), T, H, ctypes.c_float(h.eps),
+                                       _DT[h.dtype], _stream()), "scale_rows")
         self.launches += 1
         return out
 
@@ -198,6 +247,9 @@ class CudaKernels:
         the CUDA-core product.  bfloat16 runs with up to 128 rows use the tcgen05 weight-streaming
         kernel; with `allow_partial` a narrow product is split over K and comes back as a
         PartialSum for a consumer that adds the slices itself.  More rows go to cuBLAS."""
+        rows = a if isinstance(a, ScaledRows) else None
+        if rows is not None:
+            a = rows.pre
         _need(a.dtype == w.dtype, f"linear: activations are {a.dtype}, weights {w.dtype}")
         _need(a.is_contiguous() and w.is_contiguous(), "linear: operands must be contiguous")
         T, K = a.shape
@@ -206,6 +258,8 @@ class CudaKernels:
         out_dtype = out_dtype or a.dtype
         if T == 0:
             return torch.empty((T, N), dtype=out_dtype, device=a.device)
+        if rows is not None and not (T <= self.SKINNY_MAX_ROWS and K % 8 == 0 and w.data_ptr() % 16 == 0):
+            a, rows = self.materialize_rows(rows), None
         if a.dtype == torch.float32:
             _need(out_dtype == torch.float32, "linear: a float32 product gives float32")
             out = torch.empty((T, N), dtype=out_dtype, device=a.device)
@@ -218,10 +272,10 @@ class CudaKernels:
             kblocks = -(-K // 64)
             splits = max(1, min(296 // tiles, 10, kblocks // 4)) if allow_partial and bias is None else 1
             if splits > 1:
-                parts = self.linear_skinny(a, w, None, splits=splits, mode=1)
+                parts = self.linear_skinny(a, w, None, splits=splits, mode=1, rows=rows)
                 return PartialSum(parts, out_dtype)
-            if tiles >= 74 or allow_partial:
-                return self.linear_skinny(a, w, bias, out_dtype=out_dtype, splits=1, mode=0)
+            if tiles >= 74 or allow_partial or rows is not None:
+                return self.linear_skinny(a, w, bias, out_dtype=out_dtype, splits=1, mode=0, rows=rows)
         out = torch.empty((T, N), dtype=out_dtype, device=a.device)
         _check(self.lib.ifx_gemm_cublas_bf16(_ptr(a), _ptr(w), _ptr(out), T, N, K, _DT[out_dtype], _stream()),
                "gemm (bfloat16)")
@@ -233,12 +287,15 @@ class CudaKernels:
     def linear_swiglu(self, a, w_gate_up):
         """silu(a . Wg^T) * (a . Wu^T) with Wg and Wu stacked in w_gate_up [2 I, K]: one kernel
         with both accumulators for few rows, else the product followed by the activation kernel."""
+        rows = a if isinstance(a, ScaledRows) else None
+        if rows is not None:
+            a = rows.pre
         T, K = a.shape
         inter = w_gate_up.shape[0] // 2
         if (a.dtype == torch.bfloat16 and 0 < T <= self.SKINNY_MAX_ROWS and K % 8 == 0 and a.data_ptr() % 16 == 0
                 and w_gate_up.data_ptr() % 16 == 0):
-            return self.linear_skinny(a, w_gate_up, None, splits=1, mode=2, n_out=inter, up_row_offset=inter)
-        return self.silu_mul(self.linear(a, w_gate_up))
+            return self.linear_skinny(a, w_gate_up, None, splits=1, mode=2, n_out=inter, up_row_offset=inter, rows=rows)
+        return self.silu_mul(self.linear(self.materialize_rows(rows) if rows is not None else a, w_gate_up))
 
     def check_errors(self):
         """Raise if a kernel reported that one of its bounded waits ran out (reads the device flag)."""
@@ -247,9 +304,10 @@ class CudaKernels:
             self.error_flag.zero_()
             raise KernelError(f"a kernel gave up waiting on a barrier (code {code}); its output is not valid")
 
-    def linear_skinny(self, a, w, bias=None, out_dtype=None, splits=1, mode=0, n_out=None, up_row_offset=0):
+    def linear_skinny(self, a, w, bias=None, out_dtype=None, splits=1, mode=0, n_out=None, up_row_offset=0, rows=None):
         """The tcgen05 weight-streaming product for up to 128 token rows.
-        mode 0: out[T, N] (+bias); mode 1: float32 partial sums [splits, T, N]; mode 2: silu(gate) * up."""
+        mode 0: out[T, N] (+bias); mode 1: float32 partial sums [splits, T, N]; mode 2: silu(gate) * up.
+        `rows`: the ScaledRows whose `pre` is `a`; the product then applies their row scale."""
         T, K = a.shape
         N = n_out if n_out is not None else w.shape[0]
         _need(a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16, "linear_skinny: bfloat16 only")
@@ -262,6 +320,9 @@ class CudaKernels:
             out = torch.empty((T, N), dtype=out_dtype, device=a.device)
         _check(self.lib.ifx_gemm_skinny(_ptr(a), _ptr(w), _ptr(bias), _ptr(out), _ptr(partials), T, N, K, w.shape[0],
                                         splits, mode, up_row_offset, int(out_dtype == torch.float32),
+                                        _ptr(None if rows is None else rows.sumsq),
+                                        0 if rows is None else rows.sumsq.shape[1],
+                                        ctypes.c_float(0.0 if rows is None else rows.eps),
                                         _ptr(self.error_flag), _stream()), "gemm_skinny")
         self.launches += 1
         return partials if mode == 1 else out

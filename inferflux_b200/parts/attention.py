@@ -27,6 +27,9 @@ class Attention(Mixer):
     position (a PartSpec of role `position`, or None), qkv_bias (True, False or
     "if_present"), scale (None for 1/sqrt(head_dim))."""
 
+    takes_scaled_rows = True          # h goes only into the stacked projection
+
+
     def __init__(self, spec):
         super().__init__(spec)
         p = spec.params
@@ -81,7 +84,7 @@ class Attention(Mixer):
     def forward(self, h, ctx, cache):
         k = ctx.kernels
         qkv = k.linear(h, self.w_qkv, allow_partial=True)                    # [T, (nq + 2 nkv) d], maybe in K slices
-        rotary = self.position.rotary(h.device) if self.position is not None else None
+        rotary = self.position.rotary(ctx.device) if self.position is not None else None
         q = k.rope_append(qkv, self.b_qkv, rotary, self.nq, self.nkv, self.d, ctx, cache)   # [T, nq d]
         a = k.attention(q, self.nq, self.nkv, self.d, self.window, self.scale, ctx, cache)  # [T, nq d]
         return k.linear(a, self.w_o, allow_partial=True)

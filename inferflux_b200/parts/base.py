@@ -64,6 +64,10 @@ class Part:
     # False for a part whose forward reads device data on the host or launches work whose
     # shape depends on the data: a step that holds such a part is never captured into a CUDA graph.
     graph_safe = True
+    # True for a mixer or feed-forward that hands its input `h` only to `ctx.kernels.linear` /
+    # `linear_swiglu`: the norm in front may then leave its row scale to that product
+    # (`h` arrives as the kernels' pre-normed rows instead of a tensor).
+    takes_scaled_rows = False
 
     def __init__(self, spec: PartSpec):
         self.spec = spec
@@ -78,7 +82,8 @@ class Part:
 
 
 class Norm(Part):
-    def forward(self, x: torch.Tensor, delta: Optional[torch.Tensor], ctx) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, delta: Optional[torch.Tensor], ctx, lazy: bool = False) -> torch.Tensor:
+        """`lazy`: the consumer takes pre-normed rows (see Part.takes_scaled_rows)."""
         raise NotImplementedError
 
 

@@ -10,8 +10,8 @@ from .base import Block, register_part
 @register_part("block", "prenorm")
 class PreNormBlock(Block):
     def forward(self, x, pending, ctx, cache):
-        h = self.norm_mixer.forward(x, pending, ctx)          # x += pending; h = norm(x)
+        h = self.norm_mixer.forward(x, pending, ctx, lazy=self.mixer.takes_scaled_rows)   # x += pending; h = norm(x)
         a = self.mixer.forward(h, ctx, cache)
-        h = self.norm_ffn.forward(x, a, ctx)                  # x += a; h = norm(x)
+        h = self.norm_ffn.forward(x, a, ctx, lazy=self.ffn.takes_scaled_rows)             # x += a; h = norm(x)
         f = self.ffn.forward(h, ctx)
         return x, f

@@ -13,6 +13,9 @@ from .base import FeedForward, register_part
 class SwiGLU(FeedForward):
     """params: hidden_size, intermediate_size."""
 
+    takes_scaled_rows = True          # h goes only into the stacked projection
+
+
     def __init__(self, spec):
         super().__init__(spec)
         self.hidden = int(spec.params["hidden_size"])

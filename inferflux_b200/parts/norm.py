@@ -25,7 +25,9 @@ class RMSNorm(Norm):
     def load(self, tensors, dtype, device):
         self.weight = tensors["weight"].to(device=device, dtype=torch.float32).contiguous()
 
-    def forward(self, x, delta, ctx):
+    def forward(self, x, delta, ctx, lazy=False):
+        if lazy and hasattr(ctx.kernels, "prenorm"):
+            return ctx.kernels.prenorm(x, delta, self.weight, self.eps, ctx.dtype)
         if delta is None:
             return ctx.kernels.rmsnorm(x, self.weight, self.eps, ctx.dtype)
         return ctx.kernels.add_rmsnorm(x, delta, self.weight, self.eps, ctx.dtype)

@@ -134,6 +134,44 @@ def test_gemm_tcgen05_few_rows(cuda_kernels, M, N, K):
     cuda_kernels.check_errors()
 
 
+@pytest.mark.parametrize("T,H,N", [(1, 64, 128), (8, 3584, 512), (33, 1000, 264), (128, 520, 130)])
+def test_prenormed_rows_through_the_product(cuda_kernels, T, H, N):
+    """The norm that leaves its row scale to the product: prenorm + linear equals
+    add_rmsnorm + linear, for every epilogue of the few-rows product."""
+    from inferflux_b200.csrc import PartialSum, ScaledRows
+    x = rnd(T, H, seed=30)
+    parts = PartialSum(rnd(3, T, H, seed=31, scale=0.3), torch.bfloat16)
+    wn = 1 + rnd(H, seed=32, scale=0.2)
+    w = rnd(N, H, dtype=torch.bfloat16, seed=33, scale=0.1)
+    b = rnd(N, seed=34)
+    x1, x2 = x.clone(), x.clone()
+    rows = cuda_kernels.prenorm(x1, parts, wn, 1e-5, torch.bfloat16)
+    assert isinstance(rows, ScaledRows)
+    xs = x.double() + parts.parts.double().sum(0)
+    hn = PlainKernels(wide=True).rmsnorm(xs, wn, 1e-5, torch.float64)
+    close(x1, xs, atol=1e-5, rtol=1e-6)
+    close(cuda_kernels.materialize_rows(rows), hn, atol=2e-3, rtol=2 ** -7)
+    # the product works on the rounded rows x * w; its result is exact up to float32 accumulation
+    scale = torch.rsqrt((xs * xs).mean(-1, keepdim=True) + 1e-5)
+    want = (rows.pre.double() * scale) @ w.double().t()
+    close(want, hn @ w.double().t(), atol=2e-3 * math.sqrt(H), rtol=2e-2)
+    tol = 1e-4 * math.sqrt(H)
+    close(cuda_kernels.linear(rows, w, b, out_dtype=torch.float32), want + b.double(), atol=tol, rtol=1e-5)
+    close(cuda_kernels.materialize(cuda_kernels.linear(rows, w, allow_partial=True)), want, atol=tol, rtol=2 ** -8)
+    if N % 2 == 0:
+        g, u = want[:, :N // 2], want[:, N // 2:]
+        close(cuda_kernels.linear_swiglu(rows, w), g / (1 + torch.exp(-g)) * u, atol=tol, rtol=2 ** -7)
+    # a plain tensor delta and no delta at all
+    d16 = rnd(T, H, dtype=torch.bfloat16, seed=35)
+    r2 = cuda_kernels.prenorm(x2, d16, wn, 1e-5, torch.bfloat16)
+    close(cuda_kernels.materialize_rows(r2), PlainKernels(wide=True).rmsnorm(x.double() + d16.double(), wn, 1e-5, torch.float64),
+          atol=2e-3, rtol=2 ** -7)
+    r3 = cuda_kernels.prenorm(x2, None, wn, 1e-5, torch.bfloat16)
+    close(cuda_kernels.materialize_rows(r3), PlainKernels(wide=True).rmsnorm(x2.double(), wn, 1e-5, torch.float64),
+          atol=2e-3, rtol=2 ** -7)
+    cuda_kernels.check_errors()
+
+
 def test_rope_append_from_partial_sums(cuda_kernels):
     from inferflux_b200.csrc import PartialSum
     from inferflux_b200.parts.base import RotaryTable
