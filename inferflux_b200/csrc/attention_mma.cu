@@ -65,6 +65,13 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], 
       : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+// 2^x in one MUFU instruction (flushes denormal results to zero, which is what a softmax weight
+// that small should be); ex2(-inf) = 0.
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
@@ -91,7 +98,7 @@ struct PageMap {
 };
 
 // ------------------------------------------------------------- prompt portions
-template <int D>
+template <int D, int KT>
 __global__ void __launch_bounds__(128)
 attn_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kv_pool, const int* __restrict__ block_table,
                     const int* __restrict__ tiles, const int* __restrict__ req_slot, bf16* __restrict__ out, int nq,
@@ -101,9 +108,9 @@ attn_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kv_pool
   constexpr int CPR = D / 8;            // 16-byte chunks per row
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* q_s = reinterpret_cast<bf16*>(smem_raw);        // [64][LDS]
-  bf16* k_s = q_s + 64 * LDS;                           // [2][64][LDS]
-  bf16* v_s = k_s + 2 * 64 * LDS;                       // [2][64][LDS]
-  int* tbl_s = reinterpret_cast<int*>(v_s + 2 * 64 * LDS);   // [tbl_cap] block-table entries of this tile's keys
+  bf16* k_s = q_s + 64 * LDS;                           // [2][KT][LDS]
+  bf16* v_s = k_s + 2 * KT * LDS;                       // [2][KT][LDS]
+  int* tbl_s = reinterpret_cast<int*>(v_s + 2 * KT * LDS);   // [tbl_cap] block-table entries of this tile's keys
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int* tile = tiles + (size_t)blockIdx.x * 4;
@@ -115,7 +122,7 @@ attn_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kv_pool
 
   const int kfirst = window > 0 ? max(0, pos0 - window + 1) : 0;
   const int kend = pos0 + rows;
-  const int tile_begin = kfirst >> 6, tile_end = (kend + 63) >> 6;
+  const int tile_begin = kfirst / KT, tile_end = (kend + KT - 1) / KT;
   {   // the block-table entries of keys [kfirst, kend) go to shared memory once
     const int b0 = kfirst / page_size, b1 = (kend - 1) / page_size;
     if (b1 - b0 + 1 <= tbl_cap) {
@@ -135,11 +142,11 @@ attn_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kv_pool
       *reinterpret_cast<uint4*>(dst) = make_uint4(0u, 0u, 0u, 0u);
   }
   auto load_tile = [&](int t, int stage) {
-    for (int i = tid; i < 64 * CPR; i += 128) {
+    for (int i = tid; i < KT * CPR; i += 128) {
       const int row = i / CPR, c = i % CPR;
-      const int k = t * 64 + row;
-      bf16* kd = k_s + (stage * 64 + row) * LDS + c * 8;
-      bf16* vd = v_s + (stage * 64 + row) * LDS + c * 8;
+      const int k = t * KT + row;
+      bf16* kd = k_s + (stage * KT + row) * LDS + c * 8;
+      bf16* vd = v_s + (stage * KT + row) * LDS + c * 8;
       if (k >= kfirst && k < kend) {
         const bf16* src = kv_pool + pm.key_row(k, D) + c * 8;
         cp_async16(smem_u32(kd), src);
@@ -174,15 +181,15 @@ attn_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kv_pool
         ldmatrix_x4(qf[kk], smem_u32(q_s + row * LDS + col));
       }
     }
-    const bf16* kt = k_s + stage * 64 * LDS;
-    const bf16* vt = v_s + stage * 64 * LDS;
-    float s[8][4];
+    const bf16* kt = k_s + stage * KT * LDS;
+    const bf16* vt = v_s + stage * KT * LDS;
+    float s[KT / 8][4];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.0f;
+    for (int i = 0; i < KT / 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.0f;
 #pragma unroll
     for (int kk = 0; kk < D / 16; ++kk) {
 #pragma unroll
-      for (int n2 = 0; n2 < 4; ++n2) {
+      for (int n2 = 0; n2 < KT / 16; ++n2) {
         uint32_t b[4];
         const int row = n2 * 16 + (lane >> 4) * 8 + (lane & 7), col = kk * 16 + ((lane >> 3) & 1) * 8;
         ldmatrix_x4(b, smem_u32(kt + row * LDS + col));
@@ -190,16 +197,26 @@ attn_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kv_pool
         mma_bf16(s[2 * n2 + 1], qf[kk], b[2], b[3]);
       }
     }
-    // mask, scale, running maximum
+    // Masking only where a key of the tile can be invisible to a row of this warp: a tile that lies
+    // wholly inside every row's range (most tiles of a long prompt) skips the compares.
+    const int key0 = t * KT;
+    const bool inside = key0 + KT - 1 <= pos0 + warp * 16 && key0 >= kfirst &&
+                        (window <= 0 || key0 >= pos0 + warp * 16 + 15 - window + 1);
+    if (!inside) {
+#pragma unroll
+      for (int n = 0; n < KT / 8; ++n) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int key = key0 + n * 8 + 2 * (lane & 3) + (e & 1);
+          const bool ok = e < 2 ? (key <= p_lo && key >= w_lo) : (key <= p_hi && key >= w_hi);
+          if (!ok) s[n][e] = -INFINITY;
+        }
+      }
+    }
+    // running maximum of the raw scores; the scale (positive) goes into the exponent's multiply-add
     float mx_lo = -INFINITY, mx_hi = -INFINITY;
 #pragma unroll
-    for (int n = 0; n < 8; ++n) {
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int key = t * 64 + n * 8 + 2 * (lane & 3) + (e & 1);
-        const bool ok = e < 2 ? (key <= p_lo && key >= w_lo) : (key <= p_hi && key >= w_hi);
-        s[n][e] = ok ? s[n][e] * scale_log2 : -INFINITY;
-      }
+    for (int n = 0; n < KT / 8; ++n) {
       mx_lo = fmaxf(mx_lo, fmaxf(s[n][0], s[n][1]));
       mx_hi = fmaxf(mx_hi, fmaxf(s[n][2], s[n][3]));
     }
@@ -209,7 +226,8 @@ attn_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kv_pool
     mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
     const float mn_lo = fmaxf(m_lo, mx_lo), mn_hi = fmaxf(m_hi, mx_hi);
     const float mu_lo = mn_lo == -INFINITY ? 0.0f : mn_lo, mu_hi = mn_hi == -INFINITY ? 0.0f : mn_hi;
-    const float c_lo = exp2f(m_lo - mu_lo), c_hi = exp2f(m_hi - mu_hi);
+    const float c_lo = fast_exp2((m_lo - mu_lo) * scale_log2), c_hi = fast_exp2((m_hi - mu_hi) * scale_log2);
+    const float b_lo = -mu_lo * scale_log2, b_hi = -mu_hi * scale_log2;
     m_lo = mn_lo;
     m_hi = mn_hi;
     l_lo *= c_lo;
@@ -221,18 +239,18 @@ attn_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kv_pool
       o[i][2] *= c_hi;
       o[i][3] *= c_hi;
     }
-    uint32_t pa[4][4];
+    uint32_t pa[KT / 16][4];
 #pragma unroll
-    for (int n = 0; n < 8; ++n) {
-      const float e0 = exp2f(s[n][0] - mu_lo), e1 = exp2f(s[n][1] - mu_lo);
-      const float e2 = exp2f(s[n][2] - mu_hi), e3 = exp2f(s[n][3] - mu_hi);
+    for (int n = 0; n < KT / 8; ++n) {
+      const float e0 = fast_exp2(fmaf(s[n][0], scale_log2, b_lo)), e1 = fast_exp2(fmaf(s[n][1], scale_log2, b_lo));
+      const float e2 = fast_exp2(fmaf(s[n][2], scale_log2, b_hi)), e3 = fast_exp2(fmaf(s[n][3], scale_log2, b_hi));
       l_lo += e0 + e1;
       l_hi += e2 + e3;
       pa[n >> 1][(n & 1) * 2] = pack_bf16(e0, e1);
       pa[n >> 1][(n & 1) * 2 + 1] = pack_bf16(e2, e3);
     }
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
+    for (int j = 0; j < KT / 16; ++j) {
 #pragma unroll
       for (int d2 = 0; d2 < D / 16; ++d2) {
         uint32_t b[4];
@@ -851,18 +869,19 @@ template <int D>
 int launch_prefill(const bf16* q, const bf16* kv_pool, const int* block_table, const int* tiles, const int* req_slot,
                    bf16* out, int num_tiles, int nq, int nkv, int page_size, int page_shift, int max_blocks,
                    int num_pages, int window, float scale_log2, int max_keys, cudaStream_t stream) {
-  constexpr int tile_bytes = (64 + 4 * 64) * (D + 8) * 2;
+  constexpr int KT = 64;                                // keys per tile
+  constexpr int tile_bytes = (64 + 4 * KT) * (D + 8) * 2;
   int tbl_cap = max_keys / page_size + 2;               // entries a tile can need
   if (tbl_cap > 8192) tbl_cap = 0;                      // too long to copy: look pages up in global memory
   const int smem = tile_bytes + tbl_cap * 4;
   static int configured = 0;
   if (smem > configured) {
-    cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel<D, KT>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return (int)e;
     configured = smem;
   }
   dim3 grid(num_tiles, nq);
-  attn_prefill_kernel<D><<<grid, 128, smem, stream>>>(q, kv_pool, block_table, tiles, req_slot, out, nq, nkv, page_size,
+  attn_prefill_kernel<D, KT><<<grid, 128, smem, stream>>>(q, kv_pool, block_table, tiles, req_slot, out, nq, nkv, page_size,
                                                       page_shift, max_blocks, num_pages, window, scale_log2, tbl_cap);
   IFX_CHECK_LAUNCH();
   return 0;
@@ -945,7 +964,8 @@ int ifx_attention_prefill_bf16(const void* q, const void* kv_pool, const int* bl
                                int max_blocks, int num_pages, int window, float scale, int max_keys, int* error_flag,
                                cudaStream_t stream) {
   if (num_tiles <= 0) return 0;
-  if (nq <= 0 || nkv <= 0 || nq % nkv || page_size <= 0 || max_blocks <= 0 || nq > 65535) return IFX_E_BADARG;
+  if (nq <= 0 || nkv <= 0 || nq % nkv || page_size <= 0 || max_blocks <= 0 || nq > 65535 || !(scale > 0.0f))
+    return IFX_E_BADARG;                                  // the kernels take the maximum before scaling
   const float scale_log2 = scale * 1.4426950408889634f;
   const int ps = shift_of(page_size);
 #define CALL(DD)                                                                                                   \
