@@ -95,11 +95,20 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
-def qwen7b_config():
+SHAPES = {   # the three real-sized shapes of the benchmark description
+    "7b": dict(hidden_size=3584, num_hidden_layers=28, num_attention_heads=28, num_key_value_heads=4,
+               intermediate_size=18944, vocab_size=152064, tie_word_embeddings=False),
+    "1.5b": dict(hidden_size=1536, num_hidden_layers=28, num_attention_heads=12, num_key_value_heads=2,
+                 intermediate_size=8960, vocab_size=151936, tie_word_embeddings=True),
+    "32b": dict(hidden_size=5120, num_hidden_layers=64, num_attention_heads=40, num_key_value_heads=8,
+                intermediate_size=27648, vocab_size=152064, tie_word_embeddings=False),
+}
+
+
+def qwen7b_config(shape="7b"):
     from inferflux_b200.config import Qwen2Config
-    return Qwen2Config(hidden_size=3584, num_hidden_layers=28, num_attention_heads=28, num_key_value_heads=4,
-                       head_dim=128, intermediate_size=18944, vocab_size=152064, max_position_embeddings=32768,
-                       rope_theta=1000000.0, rms_norm_eps=1e-6, tie_word_embeddings=False)
+    return Qwen2Config(head_dim=128, max_position_embeddings=32768, rope_theta=1000000.0, rms_norm_eps=1e-6,
+                       **SHAPES[shape])
 
 
 def weight_bytes(cfg, batch):
@@ -108,9 +117,7 @@ def weight_bytes(cfg, batch):
     h, i, q, kv = cfg.hidden_size, cfg.intermediate_size, cfg.num_attention_heads * cfg.head_dim, \
         cfg.num_key_value_heads * cfg.head_dim
     per_layer = 2 * (h * (q + 2 * kv) + q * h + 3 * h * i) + 4 * (q + 2 * kv) + 4 * 2 * h
-    head = 0 if cfg.tie_word_embeddings else 2 * cfg.vocab_size * h
-    if cfg.tie_word_embeddings:
-        head = 2 * cfg.vocab_size * h
+    head = 2 * cfg.vocab_size * h                       # tied or not, the head's table is read once
     return cfg.num_hidden_layers * per_layer + head + 4 * h + batch * h * 2
 
 
@@ -245,6 +252,7 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=0, help="run fewer layers than the 7B shape has (named in config)")
+    ap.add_argument("--shape", default="7b", choices=sorted(SHAPES), help="model shape (default: the 7B headline shape)")
     ap.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64")
     ap.add_argument("--no-prefill", action="store_true", help="skip the 2,048-token prefill (for profiling decode)")
     args = ap.parse_args()
@@ -263,7 +271,7 @@ def main() -> int:
     from inferflux_b200 import Engine
 
     pk = peaks()
-    cfg = qwen7b_config()
+    cfg = qwen7b_config(args.shape)
     full_layers = cfg.num_hidden_layers
     if args.layers:
         cfg.num_hidden_layers = args.layers
@@ -297,12 +305,12 @@ def main() -> int:
         "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
         "ms_per_step": round(dev_ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic: random weights N(0,0.02), uniform random token ids",
-        "config": {"model": "Qwen2.5-7B shape", "layers": cfg.num_hidden_layers, "layers_full": full_layers,
+        "config": {"model": f"Qwen2.5-{args.shape.upper()} shape", "layers": cfg.num_hidden_layers, "layers_full": full_layers,
                    "hidden": cfg.hidden_size, "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads,
                    "head_dim": cfg.head_dim, "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size,
                    "rope_theta": cfg.rope_theta, "rms_norm_eps": cfg.rms_norm_eps, "global_batch": args.batch,
                    "seq_len": CONTEXT, "context_at_timing": ctx_len, "kv_page": page, "parallelism": "single GPU",
-                   "l2": "inputs larger than L2 (14 GB of weights per step), no flush",
+                   "l2": "inputs larger than L2 (GBs of weights per step), no flush",
                    "peaks": pk["source"]},
         "clocks": clock.summary(),
         "e2e": {"value": round(args.batch * 1000.0 / e2e_ms, 1), "unit": "tokens/s",

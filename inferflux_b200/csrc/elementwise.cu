@@ -39,24 +39,55 @@ __global__ void rmsnorm_kernel(float* __restrict__ x, const void* __restrict__ d
   float* xr = x + row * hidden;
   const T* dr = ADD == 1 ? reinterpret_cast<const T*>(delta_raw) + row * hidden : nullptr;
   const float* pr = ADD == 2 ? reinterpret_cast<const float*>(delta_raw) + row * hidden : nullptr;
+  T* o = out + row * hidden;
+  const bool vec = (hidden & 3) == 0;                    // rows start 16-byte aligned then
   float ss = 0.0f;
-  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
-    float v = xr[i];
-    if (ADD == 1) {
-      v += to_f32(dr[i]);
-      xr[i] = v;
-    } else if (ADD == 2) {
-      float d = 0.0f;
-      for (int s = 0; s < num_splits; ++s) d += pr[(size_t)s * split_stride + i];
-      v += d;
-      xr[i] = v;
+  if (vec) {
+    for (int i = threadIdx.x * 4; i < hidden; i += blockDim.x * 4) {
+      float4 v = *reinterpret_cast<const float4*>(xr + i);
+      if (ADD == 1) {
+        v.x += to_f32(dr[i]); v.y += to_f32(dr[i + 1]); v.z += to_f32(dr[i + 2]); v.w += to_f32(dr[i + 3]);
+        *reinterpret_cast<float4*>(xr + i) = v;
+      } else if (ADD == 2) {
+        float4 d = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int s = 0; s < num_splits; ++s) {
+          const float4 p = *reinterpret_cast<const float4*>(pr + (size_t)s * split_stride + i);
+          d.x += p.x; d.y += p.y; d.z += p.z; d.w += p.w;
+        }
+        v.x += d.x; v.y += d.y; v.z += d.z; v.w += d.w;
+        *reinterpret_cast<float4*>(xr + i) = v;
+      }
+      ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
     }
-    ss += v * v;
+  } else {
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+      float v = xr[i];
+      if (ADD == 1) {
+        v += to_f32(dr[i]);
+        xr[i] = v;
+      } else if (ADD == 2) {
+        float d = 0.0f;
+        for (int s = 0; s < num_splits; ++s) d += pr[(size_t)s * split_stride + i];
+        v += d;
+        xr[i] = v;
+      }
+      ss += v * v;
+    }
   }
   ss = block_sum(ss, scratch);
   const float r = rsqrtf(ss / (float)hidden + eps);
-  T* o = out + row * hidden;
-  for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = from_f32<T>(xr[i] * r * w[i]);
+  if (vec) {
+    for (int i = threadIdx.x * 4; i < hidden; i += blockDim.x * 4) {
+      const float4 v = *reinterpret_cast<const float4*>(xr + i);
+      const float4 wv = *reinterpret_cast<const float4*>(w + i);
+      o[i] = from_f32<T>(v.x * r * wv.x);
+      o[i + 1] = from_f32<T>(v.y * r * wv.y);
+      o[i + 2] = from_f32<T>(v.z * r * wv.z);
+      o[i + 3] = from_f32<T>(v.w * r * wv.w);
+    }
+  } else {
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = from_f32<T>(xr[i] * r * w[i]);
+  }
 }
 
 // x += sum of K-split partial sums, then RMSNorm, spread over many blocks: block
