@@ -244,6 +244,29 @@ def time_prefill(engine, cfg, tokens, warmup, reps):
     return statistics.median(times)
 
 
+def serve_workload(engine, cfg, requests, new_tokens, seed=3):
+    """Many requests with prompts of uniform random length through the scheduler: chunked
+    prefill mixed with decode, as a server would run them.  Returns (seconds, prompt tokens,
+    generated tokens, steps, preemptions)."""
+    import torch
+    from inferflux_b200.sampling import SamplingParams
+    g = torch.Generator().manual_seed(seed)
+    lens = torch.randint(128, 2049, (requests,), generator=g).tolist()
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in lens]
+    for p in prompts:
+        engine.add_request(p, SamplingParams(temperature=0.0), max_tokens=new_tokens)
+    torch.cuda.synchronize()
+    steps0 = engine.stats.steps
+    t0 = time.perf_counter()
+    done = 0
+    while engine.has_unfinished():
+        done += len(engine.step())
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    assert done == requests, f"{done} of {requests} requests finished"
+    return dt, sum(lens), requests * new_tokens, engine.stats.steps - steps0, engine.stats.preemptions
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -253,6 +276,9 @@ def main() -> int:
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=0, help="run fewer layers than the 7B shape has (named in config)")
     ap.add_argument("--shape", default="7b", choices=sorted(SHAPES), help="model shape (default: the 7B headline shape)")
+    ap.add_argument("--serve", type=int, default=0, metavar="REQUESTS",
+                    help="instead of the decode/prefill numbers: REQUESTS prompts of 128..2048 tokens, 256 new tokens "
+                         "each, chunked prefill of 512 mixed with decode, through the scheduler")
     ap.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64")
     ap.add_argument("--no-prefill", action="store_true", help="skip the 2,048-token prefill (for profiling decode)")
     args = ap.parse_args()
@@ -277,6 +303,20 @@ def main() -> int:
         cfg.num_hidden_layers = args.layers
     dev = torch.device("cuda:0")
     page = 16
+    if args.serve:
+        n = args.serve
+        engine = Engine(config=cfg, seed=0, dtype="bfloat16", device=dev, kv_page_size=page,
+                        kv_num_pages=n * (2304 // page + 2), kv_max_batch=n, kv_max_seq=2304 + 64, max_batch_size=n,
+                        max_batch_tokens=8192, chunked_prefill_tokens=512)
+        serve_workload(engine, cfg, min(n, 8), 16)                     # warm-up: kernels, graphs, allocator
+        dt, pt, gt, steps_run, pre = serve_workload(engine, cfg, n, 256)
+        print(json.dumps({"metric": "served tokens/s (prompt + generated), chunked prefill mixed with decode",
+                          "value": round((pt + gt) / dt, 1), "generated_tok_s": round(gt / dt, 1), "unit": "tokens/s",
+                          "seconds": round(dt, 3), "steps": steps_run, "requests": n, "prompt_tokens": pt,
+                          "generated_tokens": gt, "preemptions": pre, "dtype": "bf16", "n_gpus": 1,
+                          "config": {"model": f"Qwen2.5-{args.shape.upper()} shape", "prefill_chunk": 512,
+                                     "new_tokens": 256, "kv_page": page}, "impl": "ours"}))
+        return 0
     biggest = max(args.batch, 1 if args.no_points else 64)
     pages = biggest * (CONTEXT // page + 2)
     engine = Engine(config=cfg, seed=0, dtype="bfloat16", device=dev, kv_page_size=page, kv_num_pages=pages,
