@@ -15,7 +15,7 @@ ROOT = Path(__file__).resolve().parent.parent
 
 
 def tiny_configs():
-    """Three tiny configurations that differ in every size and option.
+    """Four tiny configurations that differ in every size and option.
     A and B follow the two tiny workloads the benchmark description names; C adds a
     window on its later layers, no biases, and sizes that are no power of two."""
     from inferflux_b200.config import Qwen2Config
@@ -29,7 +29,12 @@ def tiny_configs():
                     head_dim=48, intermediate_size=200, vocab_size=777, max_position_embeddings=384,
                     rope_theta=50000.0, rms_norm_eps=3e-4, tie_word_embeddings=False,
                     use_sliding_window=True, sliding_window=21, max_window_layers=2, qkv_bias=False)
-    return {"A": (a, 4), "B": (b, 8), "C": (c, 16)}
+    # D: nothing is a multiple of 8 except the head size's 8 itself: width 100, intermediate 150,
+    # vocabulary 333, head size 24 - the sizes the tiled kernels refuse and the generic ones take.
+    d = Qwen2Config(hidden_size=100, num_hidden_layers=2, num_attention_heads=3, num_key_value_heads=3,
+                    head_dim=24, intermediate_size=150, vocab_size=333, max_position_embeddings=300,
+                    rope_theta=20000.0, rms_norm_eps=1e-5, tie_word_embeddings=True)
+    return {"A": (a, 4), "B": (b, 8), "C": (c, 16), "D": (d, 16)}
 
 
 def write_tiny_model(cfg, out_dir, seed, dtype=torch.float32):

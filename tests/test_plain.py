@@ -63,7 +63,7 @@ def test_causality_and_precision_of_the_whole_model(name, loaded, tiny_configs):
         assert torch.allclose(other[:21], full[:21], atol=1e-10) and float((other[30:] - full[30:]).abs().max()) > 1e-3
 
 
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 @pytest.mark.parametrize("cutting", ["whole", "tail", "portions", "mixed"])
 def test_engine_host_logic_on_plain_kernels(name, cutting, model_dirs, tiny_configs):
     from inferflux_b200.engine import ModelRunner

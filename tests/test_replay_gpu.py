@@ -55,7 +55,7 @@ def oracle(model_dirs, tiny_configs):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 @pytest.mark.parametrize("cutting", ["whole", "tail", "portions", "mixed"])
 def test_step_function_cuttings(name, dtype, cutting, model_dirs, tiny_configs, oracle, cuda_kernels):
     cfg, page = tiny_configs[name]
@@ -74,7 +74,7 @@ def test_step_function_cuttings(name, dtype, cutting, model_dirs, tiny_configs, 
         assert g0["free"] == g0["pages"]
 
 
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_float32_is_the_same_under_every_cutting(name, model_dirs, tiny_configs, cuda_kernels):
     """The 32-bit kernels add in an order that depends on the position only, so
     every cutting gives the same bits."""
@@ -91,7 +91,7 @@ def test_float32_is_the_same_under_every_cutting(name, model_dirs, tiny_configs,
             assert np.array_equal(results[0][rid], other[rid]), f"request {rid} differs between cuttings"
 
 
-@pytest.mark.parametrize("name,dtype", [("B", "float32"), ("C", "bfloat16"), ("A", "bfloat16")])
+@pytest.mark.parametrize("name,dtype", [("B", "float32"), ("C", "bfloat16"), ("A", "bfloat16"), ("D", "bfloat16")])
 def test_trace_run_program(name, dtype, model_dirs, tiny_configs, oracle, tmp_path):
     """bin/trace_run as a user calls it: one process, all four cuttings one after the other."""
     cfg, _page = tiny_configs[name]
