@@ -113,8 +113,10 @@ attn_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kv_pool
   int* tbl_s = reinterpret_cast<int*>(v_s + 2 * KT * LDS);   // [tbl_cap] block-table entries of this tile's keys
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int* tile = tiles + (size_t)blockIdx.x * 4;
-  const int r = tile[0], row0 = tile[1], rows = tile[2], pos0 = tile[3];
+  const int* tile = tiles + (size_t)(blockIdx.x >> 1) * 4;   // a work item has up to 128 rows: two blocks
+  const int half = (blockIdx.x & 1) * 64;
+  if (tile[2] <= half) return;
+  const int r = tile[0], row0 = tile[1] + half, rows = min(64, tile[2] - half), pos0 = tile[3] + half;
   const int h = blockIdx.y;
   const int* table_g = block_table + (size_t)req_slot[r] * max_blocks;
   PageMap pm{table_g, 0, page_size, page_shift, num_pages, nkv, h / (nq / nkv)};
@@ -839,32 +841,6 @@ int launch_decode_tma(const CUtensorMap& pool_map, const bf16* q, const int* blo
                     num_pages, window, scale_log2, tbl_cap, error_flag);
 }
 
-// Tensor maps of cache pools (one per layer's pool), made once and kept.
-static int pool_map_for(CUtensorMap* out, const void* base, long long rows, int d) {
-  struct Key {
-    const void* base;
-    long long rows;
-    int d;
-    bool operator==(const Key& o) const { return base == o.base && rows == o.rows && d == o.d; }
-  };
-  struct Hash {
-    size_t operator()(const Key& k) const { return std::hash<const void*>()(k.base) ^ (size_t)k.rows * 31u ^ (size_t)k.d; }
-  };
-  static std::unordered_map<Key, CUtensorMap, Hash> cache;
-  static std::mutex mu;
-  std::lock_guard<std::mutex> lock(mu);
-  Key key{base, rows, d};
-  auto it = cache.find(key);
-  if (it == cache.end()) {
-    CUtensorMap m;
-    int rc = make_tensor_map_bf16(&m, base, rows, d, 16);
-    if (rc) return rc;
-    it = cache.emplace(key, m).first;
-  }
-  *out = it->second;
-  return 0;
-}
-
 template <int D>
 int launch_prefill(const bf16* q, const bf16* kv_pool, const int* block_table, const int* tiles, const int* req_slot,
                    bf16* out, int num_tiles, int nq, int nkv, int page_size, int page_shift, int max_blocks,
@@ -880,7 +856,7 @@ int launch_prefill(const bf16* q, const bf16* kv_pool, const int* block_table, c
     if (e != cudaSuccess) return (int)e;
     configured = smem;
   }
-  dim3 grid(num_tiles, nq);
+  dim3 grid(num_tiles * 2, nq);
   attn_prefill_kernel<D, KT><<<grid, 128, smem, stream>>>(q, kv_pool, block_table, tiles, req_slot, out, nq, nkv, page_size,
                                                       page_shift, max_blocks, num_pages, window, scale_log2, tbl_cap);
   IFX_CHECK_LAUNCH();
@@ -957,7 +933,7 @@ int ifx_attention_mma_supports(int d) {
   return d == 16 || d == 32 || d == 48 || d == 64 || d == 80 || d == 96 || d == 112 || d == 128 || d == 256;
 }
 
-// tiles: int32 [num_tiles, 4] = (request index, first flat row, rows <= 64, first position).
+// tiles: int32 [num_tiles, 4] = (request index, first flat row, rows <= 128, first position).
 // max_keys: no request of the step holds more keys than this (sizes the shared-memory copy of the block table).
 int ifx_attention_prefill_bf16(const void* q, const void* kv_pool, const int* block_table, const int* tiles,
                                const int* req_slot, void* out, int num_tiles, int nq, int nkv, int d, int page_size,
@@ -994,7 +970,7 @@ int ifx_attention_decode_bf16(const void* q, const void* kv_pool, const int* blo
   if (ps >= 4 && d % 64 == 0 && error_flag != nullptr) {       // pages of 16, 32, ... tokens: the TMA kernel
     CUtensorMap pool_map;
     const long long rows = (long long)num_pages * 2 * nkv * page_size;
-    int rc = pool_map_for(&pool_map, kv_pool, rows, d);
+    int rc = pool_tensor_map(&pool_map, kv_pool, rows, d);
     if (rc) return rc;
 #define CALL_TMA(DD)                                                                                              \
   return launch_decode_tma<DD>(pool_map, (const bf16*)q, block_table, (const int4*)decode_meta, (bf16*)out,       \

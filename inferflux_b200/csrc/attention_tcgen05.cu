@@ -1,0 +1,425 @@
+// Attention of prompt portions on the 5th-generation tensor cores.
+//
+// A thread block takes 128 query tokens of one query head and walks the keys they may
+// see in tiles of 128.  Tensor memory holds two score tiles and the output:
+//
+//   S = Q . K^T     tcgen05.mma, M 128 (queries = TMEM lanes) x N 128 (keys), K = head size;
+//                   Q and the key tile are K-major in shared memory (128-byte swizzle).  The
+//                   next tile's S goes to the other score buffer while this one is in use.
+//   softmax         four warps, one thread per query row: the row of S is read from TMEM
+//                   (tcgen05.ld), masked on edge tiles, exponentiated against a reference
+//                   maximum (log2 domain, one FFMA + one ex2 per score), and written back
+//                   over S as bfloat16 pairs (tcgen05.st): the A operand of the next product
+//   O += P . V      tcgen05.mma with A from tensor memory; V stays as the cache holds it
+//                   (key-major rows), i.e. an MN-major B operand.  O accumulates in TMEM.
+//
+// The reference maximum of a row moves only when the running maximum has outgrown it by
+// more than 2^8; then the row of O is rescaled in TMEM.  Probabilities therefore stay below
+// 2^8, and the sum and the output are taken against the same reference, so the result is
+// the softmax exactly (up to rounding).
+//
+// Warp 0 fetches: the query tile once, then per key tile the pages of K and V as TMA boxes
+// [16 keys x 64 elements] through the block table, into a ring of stages.  Warp 1 issues the
+// MMAs.  Warps 2-5 are the softmax warps.
+//
+// Keys outside a row's range get weight zero; what the cache holds there is finite (the pool
+// starts as zeros and only finite values are written to it).  Page sizes: powers of two from
+// 16; head sizes 64 and 128.  Every wait is bounded; a wait that runs out sets *error_flag.
+#include "common.cuh"
+#include "ptx_sm100.cuh"
+
+namespace ifx {
+
+typedef __nv_bfloat16 bf16;
+
+constexpr int kBM = 128;      // queries per block
+constexpr int kBN = 128;      // keys per tile
+
+__device__ __forceinline__ uint64_t desc_kmajor_sw128(uint32_t addr) {
+  // rows of 128 bytes, 8-row groups 1024 bytes apart
+  return (uint64_t)((addr & 0x3FFFFu) >> 4) | (1ull << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) |
+         (2ull << 61);
+}
+__device__ __forceinline__ uint64_t desc_mnmajor_sw128(uint32_t addr, uint32_t atom_stride_bytes) {
+  // 64 MN elements (128 bytes) contiguous, the next 64 `atom_stride_bytes` further; K rows 128 bytes
+  // apart, 8-row groups 1024 bytes apart
+  return (uint64_t)((addr & 0x3FFFFu) >> 4) | ((uint64_t)((atom_stride_bytes >> 4) & 0x3FFF) << 16) |
+         ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                          uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&r)[32]) {
+  uint32_t* u = reinterpret_cast<uint32_t*>(r);
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,"
+      "%29,%30,%31}, [%32];"
+      : "=r"(u[0]), "=r"(u[1]), "=r"(u[2]), "=r"(u[3]), "=r"(u[4]), "=r"(u[5]), "=r"(u[6]), "=r"(u[7]), "=r"(u[8]),
+        "=r"(u[9]), "=r"(u[10]), "=r"(u[11]), "=r"(u[12]), "=r"(u[13]), "=r"(u[14]), "=r"(u[15]), "=r"(u[16]),
+        "=r"(u[17]), "=r"(u[18]), "=r"(u[19]), "=r"(u[20]), "=r"(u[21]), "=r"(u[22]), "=r"(u[23]), "=r"(u[24]),
+        "=r"(u[25]), "=r"(u[26]), "=r"(u[27]), "=r"(u[28]), "=r"(u[29]), "=r"(u[30]), "=r"(u[31])
+      : "r"(taddr));
+}
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+__device__ __forceinline__ void umma_bf16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                             uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&u)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,"
+      "%30,%31,%32};"
+      ::"r"(taddr), "r"(u[0]), "r"(u[1]), "r"(u[2]), "r"(u[3]), "r"(u[4]), "r"(u[5]), "r"(u[6]), "r"(u[7]), "r"(u[8]),
+        "r"(u[9]), "r"(u[10]), "r"(u[11]), "r"(u[12]), "r"(u[13]), "r"(u[14]), "r"(u[15]), "r"(u[16]), "r"(u[17]),
+        "r"(u[18]), "r"(u[19]), "r"(u[20]), "r"(u[21]), "r"(u[22]), "r"(u[23]), "r"(u[24]), "r"(u[25]), "r"(u[26]),
+        "r"(u[27]), "r"(u[28]), "r"(u[29]), "r"(u[30]), "r"(u[31])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+constexpr float kRescaleStep = 8.0f;      // log2 units the maximum may outgrow its reference before O is rescaled
+constexpr uint32_t kTmemCols = 512;       // two score tiles (2 x 128) and the output (head size), as a power of two
+
+template <int D>
+struct PrefillLayout {
+  static constexpr int HALVES = D / 64;                       // 64-element (128-byte) column blocks of a head
+  static constexpr int STAGES = D == 128 ? 3 : 4;             // key/value tiles in flight
+  static constexpr uint32_t Q_BYTES = HALVES * kBM * 128;     // [half][128 rows][128 B]
+  static constexpr uint32_t K_BYTES = HALVES * kBN * 128;
+  static constexpr uint32_t STAGE_BYTES = 2 * K_BYTES;        // keys, then values
+  // barriers
+  static constexpr int B_Q = 0, B_KV_FULL = 1, B_KV_EMPTY = B_KV_FULL + STAGES, B_S_FULL = B_KV_EMPTY + STAGES,
+                       B_P_FULL = B_S_FULL + 2, B_O_FULL = B_P_FULL + 2, B_COUNT = B_O_FULL + 1;
+  static constexpr size_t SMEM = 1024 + Q_BYTES + (size_t)STAGES * STAGE_BYTES + B_COUNT * 8 + 16;
+};
+
+template <int D>
+__global__ void __launch_bounds__(192)
+attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap pool_map,
+                            const int* __restrict__ block_table, const int* __restrict__ tiles,
+                            const int* __restrict__ req_slot, bf16* __restrict__ out, int nq, int nkv, int page_size,
+                            int page_shift, int max_blocks, int num_pages, int window, float scale_log2,
+                            int* __restrict__ error_flag) {
+  using L = PrefillLayout<D>;
+  constexpr int HALVES = L::HALVES, STAGES = L::STAGES;
+  constexpr uint32_t Q_BYTES = L::Q_BYTES, K_BYTES = L::K_BYTES, STAGE_BYTES = L::STAGE_BYTES;
+  extern __shared__ unsigned char smem_dyn[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~(uintptr_t)1023);
+  const uint32_t q_s = smem_addr(smem);
+  const uint32_t kv_s = q_s + Q_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Q_BYTES + STAGES * STAGE_BYTES);
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + L::B_COUNT);
+  const uint32_t bar0 = smem_addr(bars);
+  auto bar = [&](int i) { return bar0 + 8 * i; };
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  pdl_launch_dependents();
+  if (threadIdx.x == 0) {
+    mbar_init(bar(L::B_Q), 1);
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(bar(L::B_KV_FULL + s), 1);
+      mbar_init(bar(L::B_KV_EMPTY + s), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(bar(L::B_S_FULL + b), 1);
+      mbar_init(bar(L::B_P_FULL + b), 4);
+    }
+    mbar_init(bar(L::B_O_FULL), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(tmem_holder)),
+                 "r"(kTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+  const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + 2 * kBN;
+  pdl_wait();
+
+  const int* tile = tiles + (size_t)(gridDim.x - 1 - blockIdx.x) * 4;      // the last tiles of a prompt see the most keys
+  const int r = tile[0], row0 = tile[1], rows = tile[2], pos0 = tile[3];
+  const int h = blockIdx.y;
+  const int g = h / (nq / nkv);
+  const int kfirst = window > 0 ? max(0, pos0 - window + 1) : 0;
+  const int kend = pos0 + rows;
+  const int tile_begin = kfirst / kBN, tile_end = (kend + kBN - 1) / kBN;
+  const int num_tiles = tile_end - tile_begin;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ fetching
+    const int* table = block_table + (size_t)req_slot[r] * max_blocks;
+    if (lane == 0) {
+      mbar_expect_tx(bar(L::B_Q), Q_BYTES);
+#pragma unroll
+      for (int hh = 0; hh < HALVES; ++hh) tma_load_2d(q_s + hh * kBM * 128, &q_map, h * D + hh * 64, row0, bar(L::B_Q));
+    }
+    bool ok = true;
+    int issued = 0;
+    for (int n = 0; n < num_tiles; ++n) {
+      const int s = n % STAGES;
+      // lanes 0-7 take one 16-key block each; its page is looked up before the wait for a free stage
+      const int key = (tile_begin + n) * kBN + lane * 16;
+      int page = 0, off = 0;
+      if (lane < kBN / 16 && key < kend && key + 16 > kfirst) {      // else: any valid page, its keys get weight zero
+        page = table[key >> page_shift];
+        if (page < 0 || page >= num_pages) page = 0;
+        off = key & (page_size - 1);
+      }
+      ok = __all_sync(0xffffffffu, mbar_wait(bar(L::B_KV_EMPTY + s), ((n / STAGES) & 1) ^ 1));
+      if (!ok) break;
+      const uint32_t fb = bar(L::B_KV_FULL + s);
+      if (lane == 0) mbar_expect_tx(fb, STAGE_BYTES);
+      __syncwarp();
+      if (lane < kBN / 16) {
+        const uint32_t k_dst = kv_s + s * STAGE_BYTES + lane * 2048, v_dst = k_dst + K_BYTES;
+        const int yk = ((page * 2) * nkv + g) * page_size + off;
+        const int yv = ((page * 2 + 1) * nkv + g) * page_size + off;
+#pragma unroll
+        for (int hh = 0; hh < HALVES; ++hh) {
+          tma_load_2d(k_dst + hh * kBN * 128, &pool_map, hh * 64, yk, fb);
+          tma_load_2d(v_dst + hh * kBN * 128, &pool_map, hh * 64, yv, fb);
+        }
+      }
+      issued = n + 1;
+    }
+    if (!ok && lane == 0) {
+      atomicExch(error_flag, 7);
+      for (int n = max(0, issued - STAGES); n < issued; ++n)       // let the copies in flight land
+        mbar_wait(bar(L::B_KV_FULL + n % STAGES), (n / STAGES) & 1);
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issue
+    if (lane == 0) {
+      const uint32_t idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kBN >> 3) << 17) |
+                               ((uint32_t)(kBM >> 4) << 24);                       // both operands K-major
+      const uint32_t idesc_o = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(D >> 3) << 17) |
+                               ((uint32_t)(kBM >> 4) << 24);                       // B (values) MN-major
+      bool ok = mbar_wait(bar(L::B_Q), 0);
+      auto issue_s = [&](int n) -> bool {                  // S(n) = Q . K(n)^T into score buffer n & 1
+        if (!mbar_wait(bar(L::B_KV_FULL + n % STAGES), (n / STAGES) & 1)) return false;
+        tc_fence_after();
+        const uint32_t k_src = kv_s + (n % STAGES) * STAGE_BYTES;
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) {
+          const uint32_t half = k / 4, inner = (k % 4) * 32;
+          umma_bf16(tmem_s + (n & 1) * kBN, desc_kmajor_sw128(q_s + half * kBM * 128) + (inner >> 4),
+                    desc_kmajor_sw128(k_src + half * kBN * 128) + (inner >> 4), idesc_s, k > 0 ? 1u : 0u);
+        }
+        umma_commit(bar(L::B_S_FULL + (n & 1)));
+        return true;
+      };
+      if (ok) ok = issue_s(0);
+      for (int n = 0; n < num_tiles && ok; ++n) {
+        // The next tile's scores, while the softmax warps work on this one.  Their buffer held the
+        // probabilities of tile n - 1; the product that reads those was issued before and runs first.
+        if (n + 1 < num_tiles) ok = issue_s(n + 1);
+        if (ok) ok = mbar_wait(bar(L::B_P_FULL + (n & 1)), (n >> 1) & 1);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t v_src = kv_s + (n % STAGES) * STAGE_BYTES + K_BYTES;
+        const uint32_t p_tmem = tmem_s + (n & 1) * kBN;
+#pragma unroll
+        for (int k = 0; k < kBN / 16; ++k)                 // O += P . V(n), 16 keys (8 columns of pairs) a step
+          umma_bf16_ts(tmem_o, p_tmem + k * 8, desc_mnmajor_sw128(v_src + k * 2048, kBN * 128), idesc_o,
+                       (n > 0 || k > 0) ? 1u : 0u);
+        umma_commit(bar(L::B_O_FULL));
+        umma_commit(bar(L::B_KV_EMPTY + n % STAGES));      // keys and values of this stage have been read
+      }
+      if (!ok) atomicExch(error_flag, 8);
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------------------------------------------ softmax, one row per thread
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;                  // TMEM lane = query row of the tile
+    const int pos = pos0 + row;
+    const int wfirst = window > 0 ? pos - window + 1 : 0;
+    const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+    float m_ref = -INFINITY, l_run = 0.0f;
+    bool ok = true;
+    for (int n = 0; n < num_tiles; ++n) {
+      const int key0 = (tile_begin + n) * kBN;
+      const uint32_t s_addr = tmem_s + (n & 1) * kBN + lane_addr;
+      ok = __all_sync(0xffffffffu, mbar_wait(bar(L::B_S_FULL + (n & 1)), (n >> 1) & 1));
+      if (!ok) break;
+      tc_fence_after();
+      float s[kBN];
+#pragma unroll
+      for (int c = 0; c < kBN; c += 32) tmem_ld32(s_addr + c, *reinterpret_cast<float(*)[32]>(&s[c]));
+      tmem_wait_ld();
+      const bool edge = key0 + kBN - 1 > pos0 || (window > 0 && key0 < pos0 + kBM - window);
+      if (edge) {
+#pragma unroll
+        for (int j = 0; j < kBN; ++j) {
+          const int key = key0 + j;
+          if (key > pos || key < wfirst) s[j] = -INFINITY;
+        }
+      }
+      float mx = s[0];
+#pragma unroll
+      for (int j = 1; j < kBN; ++j) mx = fmaxf(mx, s[j]);
+      // the reference maximum moves only when the row's maximum has outgrown it
+      const bool outgrown = m_ref > -INFINITY && (mx - m_ref) * scale_log2 > kRescaleStep;
+      float factor = 1.0f;
+      if (outgrown) {
+        factor = ex2((m_ref - mx) * scale_log2);
+        m_ref = mx;
+        l_run *= factor;
+      } else if (m_ref == -INFINITY) {
+        m_ref = mx;                                        // nothing accumulated for this row so far
+      }
+      if (n > 0 && __any_sync(0xffffffffu, outgrown)) {    // rescale this warp's rows of O in tensor memory
+        ok = __all_sync(0xffffffffu, mbar_wait(bar(L::B_O_FULL), (n - 1) & 1));   // the products so far are done
+        if (!ok) break;
+        tc_fence_after();
+#pragma unroll 1
+        for (int c = 0; c < D; c += 32) {
+          float t[32];
+          tmem_ld32(tmem_o + lane_addr + c, t);
+          tmem_wait_ld();
+          uint32_t u[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) u[j] = __float_as_uint(t[j] * factor);
+          tmem_st32(tmem_o + lane_addr + c, u);
+        }
+        tmem_wait_st();
+      }
+      const float bias = m_ref == -INFINITY ? 0.0f : -m_ref * scale_log2;
+      float sum = 0.0f;
+#pragma unroll
+      for (int c = 0; c < kBN; c += 64) {                  // 64 keys = 32 columns of bfloat16 pairs
+        uint32_t packed[32];
+#pragma unroll
+        for (int j = 0; j < 64; j += 2) {
+          const float p0 = ex2(fmaf(s[c + j], scale_log2, bias));
+          const float p1 = ex2(fmaf(s[c + j + 1], scale_log2, bias));
+          sum += p0 + p1;
+          __nv_bfloat162 b2 = __floats2bfloat162_rn(p0, p1);
+          packed[j >> 1] = *reinterpret_cast<uint32_t*>(&b2);
+        }
+        tmem_st32(s_addr + (c >> 1), packed);
+      }
+      l_run += sum;
+      tmem_wait_st();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(L::B_P_FULL + (n & 1)));
+    }
+    if (ok) ok = __all_sync(0xffffffffu, mbar_wait(bar(L::B_O_FULL), (num_tiles - 1) & 1));
+    if (!ok && lane == 0) atomicExch(error_flag, 9);
+    if (ok) {
+      tc_fence_after();
+      const float inv = l_run > 0.0f ? 1.0f / l_run : 0.0f;
+      bf16* dst = out + ((size_t)(row0 + row) * nq + h) * D;
+#pragma unroll 1
+      for (int c = 0; c < D; c += 32) {
+        float t[32];
+        tmem_ld32(tmem_o + lane_addr + c, t);
+        tmem_wait_ld();
+        if (row < rows) {
+#pragma unroll
+          for (int j = 0; j < 32; j += 8) {
+            uint4 v;
+            __nv_bfloat162* v2 = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) v2[i] = __floats2bfloat162_rn(t[j + 2 * i] * inv, t[j + 2 * i + 1] * inv);
+            *reinterpret_cast<uint4*>(dst + c + j) = v;
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+  }
+}
+
+template <int D>
+static int launch_prefill_tcgen05(const bf16* q, int num_tokens, const bf16* kv_pool, const int* block_table,
+                                  const int* tiles, const int* req_slot, bf16* out, int num_tiles, int nq, int nkv,
+                                  int page_size, int page_shift, int max_blocks, int num_pages, int window,
+                                  float scale_log2, int* error_flag, cudaStream_t stream) {
+  CUtensorMap q_map, pool_map;
+  int rc = make_tensor_map_bf16(&q_map, q, num_tokens, nq * D, kBM);
+  if (rc) return rc;
+  rc = pool_tensor_map(&pool_map, kv_pool, (long long)num_pages * 2 * nkv * page_size, D);
+  if (rc) return rc;
+  const size_t smem = PrefillLayout<D>::SMEM;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attn_prefill_tcgen05_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  return launch_pdl(attn_prefill_tcgen05_kernel<D>, dim3(num_tiles, nq), dim3(192), smem, stream, 1, q_map, pool_map,
+                    block_table, tiles, req_slot, out, nq, nkv, page_size, page_shift, max_blocks, num_pages, window,
+                    scale_log2, error_flag);
+}
+
+}  // namespace ifx
+
+using namespace ifx;
+
+extern "C" {
+
+// 1 if the tensor-core kernel takes this head size and page size.
+int ifx_attention_prefill_tcgen05_supports(int d, int page_size) {
+  return (d == 64 || d == 128) && page_size >= 16 && (page_size & (page_size - 1)) == 0;
+}
+
+// q [num_tokens, nq * d] bfloat16, 16-byte aligned.  tiles: int32 [num_tiles, 4] = (request index, first
+// flat row, rows <= 128, first position).
+int ifx_attention_prefill_tcgen05(const void* q, int num_tokens, const void* kv_pool, const int* block_table,
+                                  const int* tiles, const int* req_slot, void* out, int num_tiles, int nq, int nkv,
+                                  int d, int page_size, int max_blocks, int num_pages, int window, float scale,
+                                  int* error_flag, cudaStream_t stream) {
+  if (num_tiles <= 0) return 0;
+  if (!ifx_attention_prefill_tcgen05_supports(d, page_size) || nq <= 0 || nkv <= 0 || nq % nkv || max_blocks <= 0 ||
+      nq > 65535 || !(scale > 0.0f) || error_flag == nullptr)
+    return IFX_E_BADARG;
+  int ps = 0;
+  while ((1 << ps) < page_size) ++ps;
+  const float scale_log2 = scale * 1.4426950408889634f;
+  if (d == 64)
+    return launch_prefill_tcgen05<64>((const bf16*)q, num_tokens, (const bf16*)kv_pool, block_table, tiles, req_slot,
+                                      (bf16*)out, num_tiles, nq, nkv, page_size, ps, max_blocks, num_pages, window,
+                                      scale_log2, error_flag, stream);
+  return launch_prefill_tcgen05<128>((const bf16*)q, num_tokens, (const bf16*)kv_pool, block_table, tiles, req_slot,
+                                     (bf16*)out, num_tiles, nq, nkv, page_size, ps, max_blocks, num_pages, window,
+                                     scale_log2, error_flag, stream);
+}
+
+}  // extern "C"

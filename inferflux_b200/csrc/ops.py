@@ -100,6 +100,7 @@ class CudaKernels:
                    "ifx_scatter_i32", "ifx_rope_append", "ifx_attention_generic", "ifx_gemm_generic",
                    "ifx_gemm_cublas_bf16", "ifx_cublas_init", "ifx_argmax", "ifx_penalties", "ifx_logit_bias",
                    "ifx_sample", "ifx_attention_mma_supports", "ifx_attention_prefill_bf16",
+                   "ifx_attention_prefill_tcgen05", "ifx_attention_prefill_tcgen05_supports",
                    "ifx_attention_decode_bf16", "ifx_gemm_skinny", "ifx_residual_add_partial",
                    "ifx_reduce_partial", "ifx_reduce_add_rmsnorm", "ifx_argmax_chunks", "ifx_relay_i32", "ifx_prenorm", "ifx_scale_rows"):
             getattr(self.lib, fn).restype = ctypes.c_int
@@ -107,6 +108,8 @@ class CudaKernels:
             _check(self.lib.ifx_cublas_init(), "cublas init")
         if os.environ.get("INFERFLUX_B200_PDL", "1") == "0":      # for measurements: no overlap of consecutive kernels
             self.lib.ifx_set_pdl(0)
+        # prompt portions on the tcgen05 attention kernel (0: the mma.sync kernel, for comparisons)
+        self.tensor_core_prefill = os.environ.get("INFERFLUX_B200_TCGEN05_ATTENTION", "1") != "0"
         self.launches = 0            # kernels of this library launched so far
         self.library_calls = 0       # cuBLAS products called so far
         # scratch of the many-block reduce + norm: sums of squares per (row, chunk), a ticket per row
@@ -376,6 +379,7 @@ class CudaKernels:
         _need(kv is not None and table is not None, "attention: the mixer has no key/value cache")
         _need(kv.dtype == q.dtype, f"attention: cache is {kv.dtype}, queries {q.dtype}")
         _need(d % 8 == 0 and d <= 256, f"attention: head size {d} is not a multiple of 8 up to 256")
+        _need(q.is_contiguous() and q.shape[1] == nq * d, "attention: queries must be one [tokens, heads * size] block")
         out = torch.empty((T, nq * d), dtype=q.dtype, device=q.device)
         win = 0 if window is None else int(window)
         common = (cache.page_size, table.shape[1], kv.shape[0], win, ctypes.c_float(scale))
@@ -383,7 +387,14 @@ class CudaKernels:
         if not tiled:
             self._attention_generic(q, kv, table, ctx, None, T, out, nq, nkv, d, common)
             return out
-        if ctx.num_prefill_tiles:
+        if ctx.num_prefill_tiles and self.tensor_core_prefill and self.lib.ifx_attention_prefill_tcgen05_supports(
+                d, cache.page_size):
+            _check(self.lib.ifx_attention_prefill_tcgen05(
+                _ptr(q), T, _ptr(kv), _ptr(table), _ptr(ctx.prefill_tiles), _ptr(ctx.req_slot), _ptr(out),
+                ctx.num_prefill_tiles, nq, nkv, d, *common, _ptr(self.error_flag), _stream()),
+                "attention (prompt portions, tcgen05)")
+            self.launches += 1
+        elif ctx.num_prefill_tiles:
             _check(self.lib.ifx_attention_prefill_bf16(
                 _ptr(q), _ptr(kv), _ptr(table), _ptr(ctx.prefill_tiles), _ptr(ctx.req_slot), _ptr(out),
                 ctx.num_prefill_tiles, nq, nkv, d, *common, int(ctx.max_kv_len), _ptr(self.error_flag), _stream()),

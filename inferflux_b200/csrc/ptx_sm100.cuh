@@ -7,7 +7,9 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <functional>
 #include <mutex>
+#include <unordered_map>
 
 namespace ifx {
 
@@ -100,6 +102,33 @@ inline int make_tensor_map_bf16(CUtensorMap* map, const void* base, long long ro
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? 0 : 2000 + (int)r;
+}
+
+// Tensor maps of key/value pools (one per layer's pool, rows of one head's `d` elements, boxes of
+// 16 rows), made once and kept.
+inline int pool_tensor_map(CUtensorMap* out, const void* base, long long rows, int d) {
+  struct Key {
+    const void* base;
+    long long rows;
+    int d;
+    bool operator==(const Key& o) const { return base == o.base && rows == o.rows && d == o.d; }
+  };
+  struct Hash {
+    size_t operator()(const Key& k) const { return std::hash<const void*>()(k.base) ^ (size_t)k.rows * 31u ^ (size_t)k.d; }
+  };
+  static std::unordered_map<Key, CUtensorMap, Hash> cache;
+  static std::mutex mu;
+  std::lock_guard<std::mutex> lock(mu);
+  Key key{base, rows, d};
+  auto it = cache.find(key);
+  if (it == cache.end()) {
+    CUtensorMap m;
+    int rc = make_tensor_map_bf16(&m, base, rows, d, 16);
+    if (rc) return rc;
+    it = cache.emplace(key, m).first;
+  }
+  *out = it->second;
+  return 0;
 }
 
 }  // namespace ifx

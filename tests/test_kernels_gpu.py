@@ -227,8 +227,8 @@ def make_cache_case(dtype, nkv, d, page, lens, spans, num_pages, seed, shuffle=T
         if s_ == 1:
             decode_rows.append(base)
         else:
-            for off in range(0, s_, 64):
-                tiles.append([r, base + off, min(64, s_ - off), n - s_ + off])
+            for off in range(0, s_, 128):
+                tiles.append([r, base + off, min(128, s_ - off), n - s_ + off])
         base += s_
     ctx.decode_rows = torch.tensor(decode_rows, dtype=torch.int32, device=DEV)
     ctx.decode_meta = torch.tensor([[t, positions[t], slots[token_req[t]], 0] for t in decode_rows],
@@ -301,6 +301,34 @@ def test_attention_over_pages(cuda_kernels, dtype, nq, nkv, d, page, window):
     want = attention_oracle(q, stored, lens, spans, nq, nkv, d, window, scale)
     got = cuda_kernels.attention(q.view(T, nq * d), nq, nkv, d, window, scale, ctx, cache)
     close(got.cpu(), want, atol=2e-5 if dtype == torch.float32 else 2e-2, rtol=1e-5 if dtype == torch.float32 else 2e-2)
+
+
+@pytest.mark.parametrize("nq,nkv,d,page,window", [
+    (4, 2, 128, 16, None), (6, 1, 64, 16, None), (4, 4, 128, 32, 200), (3, 1, 64, 64, 129), (2, 1, 96, 16, 300)])
+def test_attention_long_portions(cuda_kernels, nq, nkv, d, page, window):
+    """Portions of several hundred tokens behind several hundred cached ones: many key tiles
+    for each tile of queries, whole ones and ragged ones, and a window that ends inside them."""
+    dtype = torch.bfloat16
+    lens = [700, 513, 1, 390]
+    spans = [300, 513, 1, 131]
+    ctx, cache, slots = make_cache_case(dtype, nkv, d, page, lens, spans, num_pages=sum(-(-n // page) for n in lens) + 5,
+                                        seed=13)
+    stored = fill_cache(cache, lens, slots, nkv, d, dtype, seed=14)
+    T = ctx.num_tokens
+    q = rnd(T, nq, d, dtype=dtype, seed=15, scale=0.3)
+    t = 0
+    for r, (n, s) in enumerate(zip(lens, spans)):
+        for pos in range(n - s, n):
+            first = max(0, pos - window + 1) if window else 0
+            target = [first, pos, (first + pos) // 2, max(first, pos - 127), max(first, pos - 128)][t % 5]
+            for h in range(nq):
+                g = h // (nq // nkv)
+                q[t, h] = (stored[r][0][target, g].float() * (12.0 / math.sqrt(d))).to(dtype).to(DEV)
+            t += 1
+    scale = 1.0 / math.sqrt(d)
+    want = attention_oracle(q, stored, lens, spans, nq, nkv, d, window, scale)
+    got = cuda_kernels.attention(q.view(T, nq * d), nq, nkv, d, window, scale, ctx, cache)
+    close(got.cpu(), want, atol=2e-2, rtol=2e-2)
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
