@@ -6,21 +6,25 @@
 //   S = Q . K^T     tcgen05.mma, M 128 (queries = TMEM lanes) x N 128 (keys), K = head size;
 //                   Q and the key tile are K-major in shared memory (128-byte swizzle).  The
 //                   next tile's S goes to the other score buffer while this one is in use.
-//   softmax         four warps, one thread per query row: the row of S is read from TMEM
-//                   (tcgen05.ld), masked on edge tiles, exponentiated against a reference
-//                   maximum (log2 domain, one FFMA + one ex2 per score), and written back
-//                   over S as bfloat16 pairs (tcgen05.st): the A operand of the next product
-//   O += P . V      tcgen05.mma with A from tensor memory; V stays as the cache holds it
-//                   (key-major rows), i.e. an MN-major B operand.  O accumulates in TMEM.
+//   softmax         two groups of four warps; a thread has one query row and one half of the
+//                   tile's keys (group 0: keys 0-63, group 1: keys 64-127).  Its scores are
+//                   read from TMEM (tcgen05.ld), masked on edge tiles, exponentiated against
+//                   the thread's reference maximum (log2 domain, one FFMA + one ex2 per
+//                   score), and written back over them as bfloat16 pairs (tcgen05.st): the A
+//                   operand of the next product
+//   O_g += P_g . V_g   tcgen05.mma with A from tensor memory, one accumulator per group; V stays
+//                   as the cache holds it (key-major rows), i.e. an MN-major B operand.
 //
-// The reference maximum of a row moves only when the running maximum has outgrown it by
-// more than 2^8; then the row of O is rescaled in TMEM.  Probabilities therefore stay below
-// 2^8, and the sum and the output are taken against the same reference, so the result is
-// the softmax exactly (up to rounding).
+// The two groups never talk to each other until the end: each has its own reference maximum,
+// sum and accumulator, and the block merges the two partial results as split attention does.
+// A reference maximum moves only when the running maximum has outgrown it by more than 2^8;
+// then the thread rescales its row of its accumulator in TMEM.  Probabilities therefore stay
+// below 2^8, and sum and output are taken against the same reference, so the result is the
+// softmax exactly (up to rounding).
 //
 // Warp 0 fetches: the query tile once, then per key tile the pages of K and V as TMA boxes
 // [16 keys x 64 elements] through the block table, into a ring of stages.  Warp 1 issues the
-// MMAs.  Warps 2-5 are the softmax warps.
+// MMAs.  Warps 2-9 are the softmax warps.
 //
 // Keys outside a row's range get weight zero; what the cache holds there is finite (the pool
 // starts as zeros and only finite values are written to it).  Page sizes: powers of two from
@@ -103,7 +107,8 @@ __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence:
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
 constexpr float kRescaleStep = 8.0f;      // log2 units the maximum may outgrow its reference before O is rescaled
-constexpr uint32_t kTmemCols = 512;       // two score tiles (2 x 128) and the output (head size), as a power of two
+constexpr uint32_t kTmemCols = 512;       // two score tiles (2 x 128) and two accumulators (2 x head size)
+constexpr int kThreads = 320;             // fetch warp, MMA warp, two softmax groups of four warps
 
 template <int D>
 struct PrefillLayout {
@@ -114,12 +119,14 @@ struct PrefillLayout {
   static constexpr uint32_t STAGE_BYTES = 2 * K_BYTES;        // keys, then values
   // barriers
   static constexpr int B_Q = 0, B_KV_FULL = 1, B_KV_EMPTY = B_KV_FULL + STAGES, B_S_FULL = B_KV_EMPTY + STAGES,
-                       B_P_FULL = B_S_FULL + 2, B_O_FULL = B_P_FULL + 2, B_COUNT = B_O_FULL + 1;
+                       B_P_FULL = B_S_FULL + 2, B_O_FULL = B_P_FULL + 4, B_COUNT = B_O_FULL + 1;
   static constexpr size_t SMEM = 1024 + Q_BYTES + (size_t)STAGES * STAGE_BYTES + B_COUNT * 8 + 16;
+  // after the last product the stages hold group 1's partial result: [128 rows][D + 1] floats, then (max, sum) per row
+  static_assert((size_t)STAGES * STAGE_BYTES >= (size_t)kBM * (D + 1) * 4 + kBM * 8, "merge area");
 };
 
 template <int D>
-__global__ void __launch_bounds__(192)
+__global__ void __launch_bounds__(kThreads)
 attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap pool_map,
                             const int* __restrict__ block_table, const int* __restrict__ tiles,
                             const int* __restrict__ req_slot, bf16* __restrict__ out, int nq, int nkv, int page_size,
@@ -147,7 +154,8 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __g
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(bar(L::B_S_FULL + b), 1);
-      mbar_init(bar(L::B_P_FULL + b), 4);
+      mbar_init(bar(L::B_P_FULL + 2 * b), 4);
+      mbar_init(bar(L::B_P_FULL + 2 * b + 1), 4);
     }
     mbar_init(bar(L::B_O_FULL), 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -165,9 +173,10 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __g
   const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + 2 * kBN;
   pdl_wait();
 
-  const int* tile = tiles + (size_t)(gridDim.x - 1 - blockIdx.x) * 4;      // the last tiles of a prompt see the most keys
+  // the last tiles of a prompt see the most keys: they go first; the heads of a tile run side by side
+  const int* tile = tiles + (size_t)(gridDim.y - 1 - blockIdx.y) * 4;
   const int r = tile[0], row0 = tile[1], rows = tile[2], pos0 = tile[3];
-  const int h = blockIdx.y;
+  const int h = blockIdx.x;
   const int g = h / (nq / nkv);
   const int kfirst = window > 0 ? max(0, pos0 - window + 1) : 0;
   const int kend = pos0 + rows;
@@ -242,15 +251,20 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __g
         // The next tile's scores, while the softmax warps work on this one.  Their buffer held the
         // probabilities of tile n - 1; the product that reads those was issued before and runs first.
         if (n + 1 < num_tiles) ok = issue_s(n + 1);
-        if (ok) ok = mbar_wait(bar(L::B_P_FULL + (n & 1)), (n >> 1) & 1);
-        if (!ok) break;
-        tc_fence_after();
         const uint32_t v_src = kv_s + (n % STAGES) * STAGE_BYTES + K_BYTES;
         const uint32_t p_tmem = tmem_s + (n & 1) * kBN;
 #pragma unroll
-        for (int k = 0; k < kBN / 16; ++k)                 // O += P . V(n), 16 keys (8 columns of pairs) a step
-          umma_bf16_ts(tmem_o, p_tmem + k * 8, desc_mnmajor_sw128(v_src + k * 2048, kBN * 128), idesc_o,
-                       (n > 0 || k > 0) ? 1u : 0u);
+        for (int grp = 0; grp < 2; ++grp) {                // O_g += P_g . V_g: 64 keys, 16 (8 columns of pairs) a step
+          if (ok) ok = mbar_wait(bar(L::B_P_FULL + 2 * (n & 1) + grp), (n >> 1) & 1);
+          if (!ok) break;
+          tc_fence_after();
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            umma_bf16_ts(tmem_o + grp * D, p_tmem + grp * 64 + k * 8,
+                         desc_mnmajor_sw128(v_src + (grp * 4 + k) * 2048, kBN * 128), idesc_o,
+                         (n > 0 || k > 0) ? 1u : 0u);
+        }
+        if (!ok) break;
         umma_commit(bar(L::B_O_FULL));
         umma_commit(bar(L::B_KV_EMPTY + n % STAGES));      // keys and values of this stage have been read
       }
@@ -258,35 +272,38 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __g
     }
     __syncwarp();
   } else {
-    // ------------------------------------------------------------------ softmax, one row per thread
+    // ------------------------------------------------------------------ softmax: one row, one half of the keys
+    const int grp = (warp - 2) >> 2;
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;                  // TMEM lane = query row of the tile
     const int pos = pos0 + row;
     const int wfirst = window > 0 ? pos - window + 1 : 0;
     const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+    const uint32_t o_addr = tmem_o + grp * D + lane_addr;
     float m_ref = -INFINITY, l_run = 0.0f;
     bool ok = true;
     for (int n = 0; n < num_tiles; ++n) {
-      const int key0 = (tile_begin + n) * kBN;
-      const uint32_t s_addr = tmem_s + (n & 1) * kBN + lane_addr;
+      const int key0 = (tile_begin + n) * kBN + grp * 64;
+      const uint32_t s_addr = tmem_s + (n & 1) * kBN + grp * 64 + lane_addr;
       ok = __all_sync(0xffffffffu, mbar_wait(bar(L::B_S_FULL + (n & 1)), (n >> 1) & 1));
       if (!ok) break;
       tc_fence_after();
-      float s[kBN];
-#pragma unroll
-      for (int c = 0; c < kBN; c += 32) tmem_ld32(s_addr + c, *reinterpret_cast<float(*)[32]>(&s[c]));
+      float s[64];
+      tmem_ld32(s_addr, *reinterpret_cast<float(*)[32]>(&s[0]));
+      tmem_ld32(s_addr + 32, *reinterpret_cast<float(*)[32]>(&s[32]));
       tmem_wait_ld();
-      const bool edge = key0 + kBN - 1 > pos0 || (window > 0 && key0 < pos0 + kBM - window);
+      const bool edge = key0 + 63 > pos0 || (window > 0 && key0 < pos0 + kBM - window);
       if (edge) {
 #pragma unroll
-        for (int j = 0; j < kBN; ++j) {
+        for (int j = 0; j < 64; ++j) {
           const int key = key0 + j;
           if (key > pos || key < wfirst) s[j] = -INFINITY;
         }
       }
-      float mx = s[0];
+      float mx4[4] = {s[0], s[1], s[2], s[3]};
 #pragma unroll
-      for (int j = 1; j < kBN; ++j) mx = fmaxf(mx, s[j]);
+      for (int j = 4; j < 64; ++j) mx4[j & 3] = fmaxf(mx4[j & 3], s[j]);
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       // the reference maximum moves only when the row's maximum has outgrown it
       const bool outgrown = m_ref > -INFINITY && (mx - m_ref) * scale_log2 > kRescaleStep;
       float factor = 1.0f;
@@ -297,53 +314,72 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __g
       } else if (m_ref == -INFINITY) {
         m_ref = mx;                                        // nothing accumulated for this row so far
       }
-      if (n > 0 && __any_sync(0xffffffffu, outgrown)) {    // rescale this warp's rows of O in tensor memory
+      if (n > 0 && __any_sync(0xffffffffu, outgrown)) {    // rescale this warp's rows of its accumulator
         ok = __all_sync(0xffffffffu, mbar_wait(bar(L::B_O_FULL), (n - 1) & 1));   // the products so far are done
         if (!ok) break;
         tc_fence_after();
 #pragma unroll 1
         for (int c = 0; c < D; c += 32) {
           float t[32];
-          tmem_ld32(tmem_o + lane_addr + c, t);
+          tmem_ld32(o_addr + c, t);
           tmem_wait_ld();
           uint32_t u[32];
 #pragma unroll
           for (int j = 0; j < 32; ++j) u[j] = __float_as_uint(t[j] * factor);
-          tmem_st32(tmem_o + lane_addr + c, u);
+          tmem_st32(o_addr + c, u);
         }
         tmem_wait_st();
       }
       const float bias = m_ref == -INFINITY ? 0.0f : -m_ref * scale_log2;
-      float sum = 0.0f;
+      float sum4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+      uint32_t packed[32];                                 // 64 keys = 32 columns of bfloat16 pairs
 #pragma unroll
-      for (int c = 0; c < kBN; c += 64) {                  // 64 keys = 32 columns of bfloat16 pairs
-        uint32_t packed[32];
-#pragma unroll
-        for (int j = 0; j < 64; j += 2) {
-          const float p0 = ex2(fmaf(s[c + j], scale_log2, bias));
-          const float p1 = ex2(fmaf(s[c + j + 1], scale_log2, bias));
-          sum += p0 + p1;
-          __nv_bfloat162 b2 = __floats2bfloat162_rn(p0, p1);
-          packed[j >> 1] = *reinterpret_cast<uint32_t*>(&b2);
-        }
-        tmem_st32(s_addr + (c >> 1), packed);
+      for (int j = 0; j < 64; j += 2) {
+        const float p0 = ex2(fmaf(s[j], scale_log2, bias));
+        const float p1 = ex2(fmaf(s[j + 1], scale_log2, bias));
+        sum4[(j >> 1) & 3] += p0 + p1;
+        __nv_bfloat162 b2 = __floats2bfloat162_rn(p0, p1);
+        packed[j >> 1] = *reinterpret_cast<uint32_t*>(&b2);
       }
-      l_run += sum;
+      tmem_st32(s_addr, packed);                           // over this thread's own scores (columns 0-31 of its 64)
+      l_run += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
       tmem_wait_st();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(bar(L::B_P_FULL + (n & 1)));
+      if (lane == 0) mbar_arrive(bar(L::B_P_FULL + 2 * (n & 1) + grp));
     }
     if (ok) ok = __all_sync(0xffffffffu, mbar_wait(bar(L::B_O_FULL), (num_tiles - 1) & 1));
     if (!ok && lane == 0) atomicExch(error_flag, 9);
-    if (ok) {
-      tc_fence_after();
-      const float inv = l_run > 0.0f ? 1.0f / l_run : 0.0f;
+    // Merge of the two groups' partial results: group 1 leaves its rows in shared memory (the stages
+    // are free after the last product), group 0 adds its own and writes the output.
+    float* merge_o = reinterpret_cast<float*>(smem + Q_BYTES);                 // [128][D + 1]
+    float2* merge_ml = reinterpret_cast<float2*>(merge_o + kBM * (D + 1));     // [128] (max, sum)
+    if (ok) tc_fence_after();
+    if (ok && grp == 1) {
+#pragma unroll 1
+      for (int c = 0; c < D; c += 32) {
+        float t[32];
+        tmem_ld32(o_addr + c, t);
+        tmem_wait_ld();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) merge_o[row * (D + 1) + c + j] = t[j];
+      }
+      merge_ml[row] = make_float2(m_ref, l_run);
+    }
+    asm volatile("bar.sync 1, 256;" ::: "memory");          // the eight softmax warps, whatever `ok` says
+    if (ok && grp == 0) {
+      const float2 other = merge_ml[row];
+      const float m = fmaxf(m_ref, other.x);
+      const float fa = m_ref == -INFINITY ? 0.0f : ex2((m_ref - m) * scale_log2);
+      const float fb = other.x == -INFINITY ? 0.0f : ex2((other.x - m) * scale_log2);
+      const float l = l_run * fa + other.y * fb;
+      const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+      const float wa = fa * inv, wb = fb * inv;
       bf16* dst = out + ((size_t)(row0 + row) * nq + h) * D;
 #pragma unroll 1
       for (int c = 0; c < D; c += 32) {
         float t[32];
-        tmem_ld32(tmem_o + lane_addr + c, t);
+        tmem_ld32(o_addr + c, t);
         tmem_wait_ld();
         if (row < rows) {
 #pragma unroll
@@ -351,7 +387,10 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __g
             uint4 v;
             __nv_bfloat162* v2 = reinterpret_cast<__nv_bfloat162*>(&v);
 #pragma unroll
-            for (int i = 0; i < 4; ++i) v2[i] = __floats2bfloat162_rn(t[j + 2 * i] * inv, t[j + 2 * i + 1] * inv);
+            for (int i = 0; i < 4; ++i) {
+              const float* o1 = merge_o + row * (D + 1) + c + j + 2 * i;
+              v2[i] = __floats2bfloat162_rn(t[j + 2 * i] * wa + o1[0] * wb, t[j + 2 * i + 1] * wa + o1[1] * wb);
+            }
             *reinterpret_cast<uint4*>(dst + c + j) = v;
           }
         }
@@ -384,7 +423,7 @@ static int launch_prefill_tcgen05(const bf16* q, int num_tokens, const bf16* kv_
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  return launch_pdl(attn_prefill_tcgen05_kernel<D>, dim3(num_tiles, nq), dim3(192), smem, stream, 1, q_map, pool_map,
+  return launch_pdl(attn_prefill_tcgen05_kernel<D>, dim3(nq, num_tiles), dim3(kThreads), smem, stream, 1, q_map, pool_map,
                     block_table, tiles, req_slot, out, nq, nkv, page_size, page_shift, max_blocks, num_pages, window,
                     scale_log2, error_flag);
 }
@@ -408,7 +447,7 @@ int ifx_attention_prefill_tcgen05(const void* q, int num_tokens, const void* kv_
                                   int* error_flag, cudaStream_t stream) {
   if (num_tiles <= 0) return 0;
   if (!ifx_attention_prefill_tcgen05_supports(d, page_size) || nq <= 0 || nkv <= 0 || nq % nkv || max_blocks <= 0 ||
-      nq > 65535 || !(scale > 0.0f) || error_flag == nullptr)
+      num_tiles > 65535 || !(scale > 0.0f) || error_flag == nullptr)
     return IFX_E_BADARG;
   int ps = 0;
   while ((1 << ps) < page_size) ++ps;
