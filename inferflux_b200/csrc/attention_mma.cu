@@ -113,8 +113,8 @@ attn_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kv_pool
   int* tbl_s = reinterpret_cast<int*>(v_s + 2 * KT * LDS);   // [tbl_cap] block-table entries of this tile's keys
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int* tile = tiles + (size_t)(blockIdx.x >> 1) * 4;   // a work item has up to 128 rows: two blocks
-  const int half = (blockIdx.x & 1) * 64;
+  const int* tile = tiles + (size_t)(blockIdx.x >> 2) * 4;   // a work item has up to 256 rows: four blocks
+  const int half = (blockIdx.x & 3) * 64;
   if (tile[2] <= half) return;
   const int r = tile[0], row0 = tile[1] + half, rows = min(64, tile[2] - half), pos0 = tile[3] + half;
   const int h = blockIdx.y;
@@ -856,7 +856,7 @@ int launch_prefill(const bf16* q, const bf16* kv_pool, const int* block_table, c
     if (e != cudaSuccess) return (int)e;
     configured = smem;
   }
-  dim3 grid(num_tiles * 2, nq);
+  dim3 grid(num_tiles * 4, nq);
   attn_prefill_kernel<D, KT><<<grid, 128, smem, stream>>>(q, kv_pool, block_table, tiles, req_slot, out, nq, nkv, page_size,
                                                       page_shift, max_blocks, num_pages, window, scale_log2, tbl_cap);
   IFX_CHECK_LAUNCH();
@@ -933,7 +933,7 @@ int ifx_attention_mma_supports(int d) {
   return d == 16 || d == 32 || d == 48 || d == 64 || d == 80 || d == 96 || d == 112 || d == 128 || d == 256;
 }
 
-// tiles: int32 [num_tiles, 4] = (request index, first flat row, rows <= 128, first position).
+// tiles: int32 [num_tiles, 4] = (request index, first flat row, rows <= 256, first position).
 // max_keys: no request of the step holds more keys than this (sizes the shared-memory copy of the block table).
 int ifx_attention_prefill_bf16(const void* q, const void* kv_pool, const int* block_table, const int* tiles,
                                const int* req_slot, void* out, int num_tiles, int nq, int nkv, int d, int page_size,

@@ -1,30 +1,29 @@
 // Attention of prompt portions on the 5th-generation tensor cores.
 //
-// A thread block takes 128 query tokens of one query head and walks the keys they may
-// see in tiles of 128.  Tensor memory holds two score tiles and the output:
+// A thread block takes up to 256 query tokens of one query head, as two tiles of 128, and
+// walks the keys they may see in tiles of 128; both query tiles use each key/value tile that
+// is fetched, which halves the traffic from L2.  Tensor memory holds, per query tile, the
+// scores and the output:
 //
 //   S = Q . K^T     tcgen05.mma, M 128 (queries = TMEM lanes) x N 128 (keys), K = head size;
-//                   Q and the key tile are K-major in shared memory (128-byte swizzle).  The
-//                   next tile's S goes to the other score buffer while this one is in use.
-//   softmax         two groups of four warps; a thread has one query row and one half of the
-//                   tile's keys (group 0: keys 0-63, group 1: keys 64-127).  Its scores are
-//                   read from TMEM (tcgen05.ld), masked on edge tiles, exponentiated against
-//                   the thread's reference maximum (log2 domain, one FFMA + one ex2 per
-//                   score), and written back over them as bfloat16 pairs (tcgen05.st): the A
+//                   Q and the key tile are K-major in shared memory (128-byte swizzle)
+//   softmax         one group of four warps per query tile, one thread per query row: the row
+//                   of S is read from TMEM (tcgen05.ld), masked on edge tiles, exponentiated
+//                   against the row's reference maximum (log2 domain, one FFMA + one ex2 per
+//                   score), and written back over S as bfloat16 pairs (tcgen05.st): the A
 //                   operand of the next product
-//   O_g += P_g . V_g   tcgen05.mma with A from tensor memory, one accumulator per group; V stays
-//                   as the cache holds it (key-major rows), i.e. an MN-major B operand.
+//   O += P . V      tcgen05.mma with A from tensor memory; V stays as the cache holds it
+//                   (key-major rows), i.e. an MN-major B operand.  O accumulates in TMEM.
 //
-// The two groups never talk to each other until the end: each has its own reference maximum,
-// sum and accumulator, and the block merges the two partial results as split attention does.
-// A reference maximum moves only when the running maximum has outgrown it by more than 2^8;
-// then the thread rescales its row of its accumulator in TMEM.  Probabilities therefore stay
-// below 2^8, and sum and output are taken against the same reference, so the result is the
-// softmax exactly (up to rounding).
+// The MMA warp alternates between the two query tiles, so that the tensor cores work on one
+// tile while the other tile's softmax runs.  A reference maximum moves only when the running
+// maximum has outgrown it by more than 2^8; then the thread rescales its row of O in TMEM.
+// Probabilities therefore stay below 2^8, and sum and output are taken against the same
+// reference, so the result is the softmax exactly (up to rounding).
 //
-// Warp 0 fetches: the query tile once, then per key tile the pages of K and V as TMA boxes
-// [16 keys x 64 elements] through the block table, into a ring of stages.  Warp 1 issues the
-// MMAs.  Warps 2-9 are the softmax warps.
+// Warp 0 fetches: the query tiles once, then per key tile the pages of K and of V as TMA boxes
+// [16 keys x 64 elements] through the block table, into a ring of slots (a slot holds the keys
+// or the values of one tile).  Warp 1 issues the MMAs.  Warps 2-5 and 6-9 are the softmax groups.
 //
 // Keys outside a row's range get weight zero; what the cache holds there is finite (the pool
 // starts as zeros and only finite values are written to it).  Page sizes: powers of two from
@@ -107,22 +106,18 @@ __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence:
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
 constexpr float kRescaleStep = 8.0f;      // log2 units the maximum may outgrow its reference before O is rescaled
-constexpr uint32_t kTmemCols = 512;       // two score tiles (2 x 128) and two accumulators (2 x head size)
+constexpr uint32_t kTmemCols = 512;       // per query tile: scores (128 columns) and output (head size)
 constexpr int kThreads = 320;             // fetch warp, MMA warp, two softmax groups of four warps
 
 template <int D>
 struct PrefillLayout {
   static constexpr int HALVES = D / 64;                       // 64-element (128-byte) column blocks of a head
-  static constexpr int STAGES = D == 128 ? 3 : 4;             // key/value tiles in flight
-  static constexpr uint32_t Q_BYTES = HALVES * kBM * 128;     // [half][128 rows][128 B]
-  static constexpr uint32_t K_BYTES = HALVES * kBN * 128;
-  static constexpr uint32_t STAGE_BYTES = 2 * K_BYTES;        // keys, then values
-  // barriers
-  static constexpr int B_Q = 0, B_KV_FULL = 1, B_KV_EMPTY = B_KV_FULL + STAGES, B_S_FULL = B_KV_EMPTY + STAGES,
-                       B_P_FULL = B_S_FULL + 2, B_O_FULL = B_P_FULL + 4, B_COUNT = B_O_FULL + 1;
-  static constexpr size_t SMEM = 1024 + Q_BYTES + (size_t)STAGES * STAGE_BYTES + B_COUNT * 8 + 16;
-  // after the last product the stages hold group 1's partial result: [128 rows][D + 1] floats, then (max, sum) per row
-  static_assert((size_t)STAGES * STAGE_BYTES >= (size_t)kBM * (D + 1) * 4 + kBM * 8, "merge area");
+  static constexpr int SLOTS = D == 128 ? 5 : 8;              // key or value tiles in flight
+  static constexpr uint32_t Q_BYTES = HALVES * kBM * 128;     // one query tile: [half][128 rows][128 B]
+  static constexpr uint32_t SLOT_BYTES = HALVES * kBN * 128;  // the keys or the values of one tile
+  static constexpr int B_Q = 0, B_FULL = 1, B_EMPTY = B_FULL + SLOTS, B_S_FULL = B_EMPTY + SLOTS,
+                       B_P_FULL = B_S_FULL + 2, B_O_FULL = B_P_FULL + 2, B_COUNT = B_O_FULL + 2;
+  static constexpr size_t SMEM = 1024 + 2 * Q_BYTES + (size_t)SLOTS * SLOT_BYTES + B_COUNT * 8 + 16;
 };
 
 template <int D>
@@ -133,13 +128,13 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __g
                             int page_shift, int max_blocks, int num_pages, int window, float scale_log2,
                             int* __restrict__ error_flag) {
   using L = PrefillLayout<D>;
-  constexpr int HALVES = L::HALVES, STAGES = L::STAGES;
-  constexpr uint32_t Q_BYTES = L::Q_BYTES, K_BYTES = L::K_BYTES, STAGE_BYTES = L::STAGE_BYTES;
+  constexpr int HALVES = L::HALVES, SLOTS = L::SLOTS;
+  constexpr uint32_t Q_BYTES = L::Q_BYTES, SLOT_BYTES = L::SLOT_BYTES;
   extern __shared__ unsigned char smem_dyn[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~(uintptr_t)1023);
-  const uint32_t q_s = smem_addr(smem);
-  const uint32_t kv_s = q_s + Q_BYTES;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Q_BYTES + STAGES * STAGE_BYTES);
+  const uint32_t q_s = smem_addr(smem);                  // two query tiles
+  const uint32_t kv_s = q_s + 2 * Q_BYTES;               // the ring of slots
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 2 * Q_BYTES + SLOTS * SLOT_BYTES);
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + L::B_COUNT);
   const uint32_t bar0 = smem_addr(bars);
   auto bar = [&](int i) { return bar0 + 8 * i; };
@@ -148,16 +143,15 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __g
   pdl_launch_dependents();
   if (threadIdx.x == 0) {
     mbar_init(bar(L::B_Q), 1);
-    for (int s = 0; s < STAGES; ++s) {
-      mbar_init(bar(L::B_KV_FULL + s), 1);
-      mbar_init(bar(L::B_KV_EMPTY + s), 1);
+    for (int s = 0; s < SLOTS; ++s) {
+      mbar_init(bar(L::B_FULL + s), 1);
+      mbar_init(bar(L::B_EMPTY + s), 1);
     }
-    for (int b = 0; b < 2; ++b) {
-      mbar_init(bar(L::B_S_FULL + b), 1);
-      mbar_init(bar(L::B_P_FULL + 2 * b), 4);
-      mbar_init(bar(L::B_P_FULL + 2 * b + 1), 4);
+    for (int q = 0; q < 2; ++q) {
+      mbar_init(bar(L::B_S_FULL + q), 1);
+      mbar_init(bar(L::B_P_FULL + q), 4);
+      mbar_init(bar(L::B_O_FULL + q), 1);
     }
-    mbar_init(bar(L::B_O_FULL), 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
@@ -170,60 +164,65 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __g
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
-  const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + 2 * kBN;
+  const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + 2 * kBN;       // S of tile q: + q * 128; O: + q * D
   pdl_wait();
 
-  // the last tiles of a prompt see the most keys: they go first; the heads of a tile run side by side
+  // the last items of a prompt see the most keys: they go first; the heads of an item run side by side
   const int* tile = tiles + (size_t)(gridDim.y - 1 - blockIdx.y) * 4;
   const int r = tile[0], row0 = tile[1], rows = tile[2], pos0 = tile[3];
   const int h = blockIdx.x;
   const int g = h / (nq / nkv);
-  const int kfirst = window > 0 ? max(0, pos0 - window + 1) : 0;
-  const int kend = pos0 + rows;
-  const int tile_begin = kfirst / kBN, tile_end = (kend + kBN - 1) / kBN;
-  const int num_tiles = tile_end - tile_begin;
+  // key tiles [tb_q, te_q) of query tile q (rows q * 128 ...); tile 1 may be absent
+  const int rows_1 = max(rows - kBM, 0);
+  const int tb_0 = (window > 0 ? max(0, pos0 - window + 1) : 0) / kBN;
+  const int te_0 = (pos0 + min(rows, kBM) + kBN - 1) / kBN;
+  const int tb_1 = (window > 0 ? max(0, pos0 + kBM - window + 1) : 0) / kBN;
+  const int te_1 = rows_1 > 0 ? (pos0 + rows + kBN - 1) / kBN : tb_1;
+  const int tb = tb_0, te = max(te_0, te_1);
+  const int kfirst = window > 0 ? max(0, pos0 - window + 1) : 0, kend = pos0 + rows;
 
   if (warp == 0) {
     // ------------------------------------------------------------------ fetching
     const int* table = block_table + (size_t)req_slot[r] * max_blocks;
     if (lane == 0) {
-      mbar_expect_tx(bar(L::B_Q), Q_BYTES);
+      mbar_expect_tx(bar(L::B_Q), rows_1 > 0 ? 2 * Q_BYTES : Q_BYTES);
+      for (int q = 0; q < (rows_1 > 0 ? 2 : 1); ++q)
 #pragma unroll
-      for (int hh = 0; hh < HALVES; ++hh) tma_load_2d(q_s + hh * kBM * 128, &q_map, h * D + hh * 64, row0, bar(L::B_Q));
+        for (int hh = 0; hh < HALVES; ++hh)
+          tma_load_2d(q_s + q * Q_BYTES + hh * kBM * 128, &q_map, h * D + hh * 64, row0 + q * kBM, bar(L::B_Q));
     }
     bool ok = true;
-    int issued = 0;
-    for (int n = 0; n < num_tiles; ++n) {
-      const int s = n % STAGES;
-      // lanes 0-7 take one 16-key block each; its page is looked up before the wait for a free stage
-      const int key = (tile_begin + n) * kBN + lane * 16;
+    int issued = 0;                                       // slots filled so far
+    for (int kt = tb; kt < te && ok; ++kt) {
+      // lanes 0-7 take one 16-key block each; its page is looked up before the wait for a free slot
+      const int key = kt * kBN + lane * 16;
       int page = 0, off = 0;
       if (lane < kBN / 16 && key < kend && key + 16 > kfirst) {      // else: any valid page, its keys get weight zero
         page = table[key >> page_shift];
         if (page < 0 || page >= num_pages) page = 0;
         off = key & (page_size - 1);
       }
-      ok = __all_sync(0xffffffffu, mbar_wait(bar(L::B_KV_EMPTY + s), ((n / STAGES) & 1) ^ 1));
-      if (!ok) break;
-      const uint32_t fb = bar(L::B_KV_FULL + s);
-      if (lane == 0) mbar_expect_tx(fb, STAGE_BYTES);
-      __syncwarp();
-      if (lane < kBN / 16) {
-        const uint32_t k_dst = kv_s + s * STAGE_BYTES + lane * 2048, v_dst = k_dst + K_BYTES;
-        const int yk = ((page * 2) * nkv + g) * page_size + off;
-        const int yv = ((page * 2 + 1) * nkv + g) * page_size + off;
+#pragma unroll 1
+      for (int kv = 0; kv < 2; ++kv) {                     // the keys, then the values
+        const int j = 2 * (kt - tb) + kv, s = j % SLOTS;
+        ok = __all_sync(0xffffffffu, mbar_wait(bar(L::B_EMPTY + s), ((j / SLOTS) & 1) ^ 1));
+        if (!ok) break;
+        const uint32_t fb = bar(L::B_FULL + s);
+        if (lane == 0) mbar_expect_tx(fb, SLOT_BYTES);
+        __syncwarp();
+        if (lane < kBN / 16) {
+          const uint32_t dst = kv_s + s * SLOT_BYTES + lane * 2048;
+          const int y = ((page * 2 + kv) * nkv + g) * page_size + off;
 #pragma unroll
-        for (int hh = 0; hh < HALVES; ++hh) {
-          tma_load_2d(k_dst + hh * kBN * 128, &pool_map, hh * 64, yk, fb);
-          tma_load_2d(v_dst + hh * kBN * 128, &pool_map, hh * 64, yv, fb);
+          for (int hh = 0; hh < HALVES; ++hh) tma_load_2d(dst + hh * kBN * 128, &pool_map, hh * 64, y, fb);
         }
+        issued = j + 1;
       }
-      issued = n + 1;
     }
     if (!ok && lane == 0) {
       atomicExch(error_flag, 7);
-      for (int n = max(0, issued - STAGES); n < issued; ++n)       // let the copies in flight land
-        mbar_wait(bar(L::B_KV_FULL + n % STAGES), (n / STAGES) & 1);
+      for (int j = max(0, issued - SLOTS); j < issued; ++j)        // let the copies in flight land
+        mbar_wait(bar(L::B_FULL + j % SLOTS), (j / SLOTS) & 1);
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issue
@@ -232,77 +231,94 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __g
                                ((uint32_t)(kBM >> 4) << 24);                       // both operands K-major
       const uint32_t idesc_o = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(D >> 3) << 17) |
                                ((uint32_t)(kBM >> 4) << 24);                       // B (values) MN-major
+      auto active = [&](int q, int kt) { return q == 0 ? (kt >= tb_0 && kt < te_0) : (kt >= tb_1 && kt < te_1); };
+      auto last_q = [&](int kt) { return active(1, kt) ? 1 : 0; };    // the query tile that uses a key tile last
       bool ok = mbar_wait(bar(L::B_Q), 0);
-      auto issue_s = [&](int n) -> bool {                  // S(n) = Q . K(n)^T into score buffer n & 1
-        if (!mbar_wait(bar(L::B_KV_FULL + n % STAGES), (n / STAGES) & 1)) return false;
+      auto issue_s = [&](int q, int kt) -> bool {         // S_q = Q_q . K(kt)^T
+        const int j = 2 * (kt - tb), s = j % SLOTS;
+        if (!mbar_wait(bar(L::B_FULL + s), (j / SLOTS) & 1)) return false;
         tc_fence_after();
-        const uint32_t k_src = kv_s + (n % STAGES) * STAGE_BYTES;
+        const uint32_t k_src = kv_s + s * SLOT_BYTES, q_src = q_s + q * Q_BYTES;
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
           const uint32_t half = k / 4, inner = (k % 4) * 32;
-          umma_bf16(tmem_s + (n & 1) * kBN, desc_kmajor_sw128(q_s + half * kBM * 128) + (inner >> 4),
+          umma_bf16(tmem_s + q * kBN, desc_kmajor_sw128(q_src + half * kBM * 128) + (inner >> 4),
                     desc_kmajor_sw128(k_src + half * kBN * 128) + (inner >> 4), idesc_s, k > 0 ? 1u : 0u);
         }
-        umma_commit(bar(L::B_S_FULL + (n & 1)));
+        umma_commit(bar(L::B_S_FULL + q));
+        if (q == last_q(kt)) umma_commit(bar(L::B_EMPTY + s));      // the keys have been read
         return true;
       };
-      if (ok) ok = issue_s(0);
-      for (int n = 0; n < num_tiles && ok; ++n) {
-        // The next tile's scores, while the softmax warps work on this one.  Their buffer held the
-        // probabilities of tile n - 1; the product that reads those was issued before and runs first.
-        if (n + 1 < num_tiles) ok = issue_s(n + 1);
-        const uint32_t v_src = kv_s + (n % STAGES) * STAGE_BYTES + K_BYTES;
-        const uint32_t p_tmem = tmem_s + (n & 1) * kBN;
+      int done[2] = {0, 0};                                // key tiles of each query tile so far
+      auto issue_pv = [&](int q, int kt) -> bool {        // O_q += P_q . V(kt)
+        const int j = 2 * (kt - tb) + 1, s = j % SLOTS;
+        if (!mbar_wait(bar(L::B_P_FULL + q), done[q] & 1) || !mbar_wait(bar(L::B_FULL + s), (j / SLOTS) & 1))
+          return false;
+        tc_fence_after();
+        const uint32_t v_src = kv_s + s * SLOT_BYTES;
 #pragma unroll
-        for (int grp = 0; grp < 2; ++grp) {                // O_g += P_g . V_g: 64 keys, 16 (8 columns of pairs) a step
-          if (ok) ok = mbar_wait(bar(L::B_P_FULL + 2 * (n & 1) + grp), (n >> 1) & 1);
-          if (!ok) break;
-          tc_fence_after();
-#pragma unroll
-          for (int k = 0; k < 4; ++k)
-            umma_bf16_ts(tmem_o + grp * D, p_tmem + grp * 64 + k * 8,
-                         desc_mnmajor_sw128(v_src + (grp * 4 + k) * 2048, kBN * 128), idesc_o,
-                         (n > 0 || k > 0) ? 1u : 0u);
+        for (int k = 0; k < kBN / 16; ++k)                 // 16 keys (8 columns of pairs) a step
+          umma_bf16_ts(tmem_o + q * D, tmem_s + q * kBN + k * 8, desc_mnmajor_sw128(v_src + k * 2048, kBN * 128),
+                       idesc_o, (done[q] > 0 || k > 0) ? 1u : 0u);
+        umma_commit(bar(L::B_O_FULL + q));
+        if (q == last_q(kt)) umma_commit(bar(L::B_EMPTY + s));      // the values have been read
+        ++done[q];
+        return true;
+      };
+      for (int q = 0; q < 2 && ok; ++q)
+        if (active(q, tb)) ok = issue_s(q, tb);
+      for (int kt = tb; kt < te && ok; ++kt) {
+        for (int q = 0; q < 2 && ok; ++q) {
+          if (!active(q, kt)) continue;
+          if (kt != tb && kt == (q == 0 ? tb_0 : tb_1)) ok = issue_s(q, kt);   // a tile that starts later (window)
+          if (ok) ok = issue_pv(q, kt);
+          // the next scores of this query tile go over its probabilities: the product that reads them
+          // was issued just before and runs first; meanwhile the other tile's softmax is at work
+          if (ok && active(q, kt + 1)) ok = issue_s(q, kt + 1);
         }
-        if (!ok) break;
-        umma_commit(bar(L::B_O_FULL));
-        umma_commit(bar(L::B_KV_EMPTY + n % STAGES));      // keys and values of this stage have been read
       }
       if (!ok) atomicExch(error_flag, 8);
     }
     __syncwarp();
   } else {
-    // ------------------------------------------------------------------ softmax: one row, one half of the keys
-    const int grp = (warp - 2) >> 2;
+    // ------------------------------------------------------------------ softmax: one query tile, one row per thread
+    const int q = (warp - 2) >> 2;
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;                  // TMEM lane = query row of the tile
-    const int pos = pos0 + row;
+    const int rows_q = q == 0 ? min(rows, kBM) : rows_1;
+    const int pos0_q = pos0 + q * kBM;
+    const int pos = pos0_q + row;
     const int wfirst = window > 0 ? pos - window + 1 : 0;
+    const int tb_q = q == 0 ? tb_0 : tb_1, te_q = q == 0 ? te_0 : te_1;
     const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
-    const uint32_t o_addr = tmem_o + grp * D + lane_addr;
+    const uint32_t s_addr = tmem_s + q * kBN + lane_addr, o_addr = tmem_o + q * D + lane_addr;
     float m_ref = -INFINITY, l_run = 0.0f;
     bool ok = true;
-    for (int n = 0; n < num_tiles; ++n) {
-      const int key0 = (tile_begin + n) * kBN + grp * 64;
-      const uint32_t s_addr = tmem_s + (n & 1) * kBN + grp * 64 + lane_addr;
-      ok = __all_sync(0xffffffffu, mbar_wait(bar(L::B_S_FULL + (n & 1)), (n >> 1) & 1));
+    int i = 0;
+    for (int kt = tb_q; kt < te_q; ++kt, ++i) {
+      const int key0 = kt * kBN;
+      ok = __all_sync(0xffffffffu, mbar_wait(bar(L::B_S_FULL + q), i & 1));
       if (!ok) break;
       tc_fence_after();
-      float s[64];
-      tmem_ld32(s_addr, *reinterpret_cast<float(*)[32]>(&s[0]));
-      tmem_ld32(s_addr + 32, *reinterpret_cast<float(*)[32]>(&s[32]));
-      tmem_wait_ld();
-      const bool edge = key0 + 63 > pos0 || (window > 0 && key0 < pos0 + kBM - window);
-      if (edge) {
+      const bool edge = key0 + kBN - 1 > pos0_q || (window > 0 && key0 < pos0_q + kBM - window);
+      // pass 1: the row's maximum
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-        for (int j = 0; j < 64; ++j) {
-          const int key = key0 + j;
-          if (key > pos || key < wfirst) s[j] = -INFINITY;
+      for (int c = 0; c < kBN; c += 64) {
+        float s[64];
+        tmem_ld32(s_addr + c, *reinterpret_cast<float(*)[32]>(&s[0]));
+        tmem_ld32(s_addr + c + 32, *reinterpret_cast<float(*)[32]>(&s[32]));
+        tmem_wait_ld();
+        if (edge) {
+#pragma unroll
+          for (int j = 0; j < 64; ++j) {
+            const int key = key0 + c + j;
+            if (key > pos || key < wfirst) s[j] = -INFINITY;
+          }
         }
-      }
-      float mx4[4] = {s[0], s[1], s[2], s[3]};
 #pragma unroll
-      for (int j = 4; j < 64; ++j) mx4[j & 3] = fmaxf(mx4[j & 3], s[j]);
+        for (int j = 0; j < 64; ++j) mx4[j & 3] = fmaxf(mx4[j & 3], s[j]);
+      }
       const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       // the reference maximum moves only when the row's maximum has outgrown it
       const bool outgrown = m_ref > -INFINITY && (mx - m_ref) * scale_log2 > kRescaleStep;
@@ -314,8 +330,8 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __g
       } else if (m_ref == -INFINITY) {
         m_ref = mx;                                        // nothing accumulated for this row so far
       }
-      if (n > 0 && __any_sync(0xffffffffu, outgrown)) {    // rescale this warp's rows of its accumulator
-        ok = __all_sync(0xffffffffu, mbar_wait(bar(L::B_O_FULL), (n - 1) & 1));   // the products so far are done
+      if (i > 0 && __any_sync(0xffffffffu, outgrown)) {    // rescale this warp's rows of O in tensor memory
+        ok = __all_sync(0xffffffffu, mbar_wait(bar(L::B_O_FULL + q), (i - 1) & 1));   // the products so far are done
         if (!ok) break;
         tc_fence_after();
 #pragma unroll 1
@@ -330,67 +346,57 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __g
         }
         tmem_wait_st();
       }
+      // pass 2: probabilities over the scores, 64 keys (32 columns of bfloat16 pairs) at a time
       const float bias = m_ref == -INFINITY ? 0.0f : -m_ref * scale_log2;
       float sum4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-      uint32_t packed[32];                                 // 64 keys = 32 columns of bfloat16 pairs
 #pragma unroll
-      for (int j = 0; j < 64; j += 2) {
-        const float p0 = ex2(fmaf(s[j], scale_log2, bias));
-        const float p1 = ex2(fmaf(s[j + 1], scale_log2, bias));
-        sum4[(j >> 1) & 3] += p0 + p1;
-        __nv_bfloat162 b2 = __floats2bfloat162_rn(p0, p1);
-        packed[j >> 1] = *reinterpret_cast<uint32_t*>(&b2);
+      for (int c = 0; c < kBN; c += 64) {
+        float s[64];
+        tmem_ld32(s_addr + c, *reinterpret_cast<float(*)[32]>(&s[0]));
+        tmem_ld32(s_addr + c + 32, *reinterpret_cast<float(*)[32]>(&s[32]));
+        tmem_wait_ld();
+        if (edge) {
+#pragma unroll
+          for (int j = 0; j < 64; ++j) {
+            const int key = key0 + c + j;
+            if (key > pos || key < wfirst) s[j] = -INFINITY;
+          }
+        }
+        uint32_t packed[32];
+#pragma unroll
+        for (int j = 0; j < 64; j += 2) {
+          const float p0 = ex2(fmaf(s[j], scale_log2, bias));
+          const float p1 = ex2(fmaf(s[j + 1], scale_log2, bias));
+          sum4[(j >> 1) & 3] += p0 + p1;
+          __nv_bfloat162 b2 = __floats2bfloat162_rn(p0, p1);
+          packed[j >> 1] = *reinterpret_cast<uint32_t*>(&b2);
+        }
+        tmem_st32(s_addr + (c >> 1), packed);              // columns whose scores have been read already
       }
-      tmem_st32(s_addr, packed);                           // over this thread's own scores (columns 0-31 of its 64)
       l_run += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
       tmem_wait_st();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(bar(L::B_P_FULL + 2 * (n & 1) + grp));
+      if (lane == 0) mbar_arrive(bar(L::B_P_FULL + q));
     }
-    if (ok) ok = __all_sync(0xffffffffu, mbar_wait(bar(L::B_O_FULL), (num_tiles - 1) & 1));
+    if (ok && i > 0) ok = __all_sync(0xffffffffu, mbar_wait(bar(L::B_O_FULL + q), (i - 1) & 1));
     if (!ok && lane == 0) atomicExch(error_flag, 9);
-    // Merge of the two groups' partial results: group 1 leaves its rows in shared memory (the stages
-    // are free after the last product), group 0 adds its own and writes the output.
-    float* merge_o = reinterpret_cast<float*>(smem + Q_BYTES);                 // [128][D + 1]
-    float2* merge_ml = reinterpret_cast<float2*>(merge_o + kBM * (D + 1));     // [128] (max, sum)
-    if (ok) tc_fence_after();
-    if (ok && grp == 1) {
+    if (ok && i > 0) {
+      tc_fence_after();
+      const float inv = l_run > 0.0f ? 1.0f / l_run : 0.0f;
+      bf16* dst = out + ((size_t)(row0 + q * kBM + row) * nq + h) * D;
 #pragma unroll 1
       for (int c = 0; c < D; c += 32) {
         float t[32];
         tmem_ld32(o_addr + c, t);
         tmem_wait_ld();
-#pragma unroll
-        for (int j = 0; j < 32; ++j) merge_o[row * (D + 1) + c + j] = t[j];
-      }
-      merge_ml[row] = make_float2(m_ref, l_run);
-    }
-    asm volatile("bar.sync 1, 256;" ::: "memory");          // the eight softmax warps, whatever `ok` says
-    if (ok && grp == 0) {
-      const float2 other = merge_ml[row];
-      const float m = fmaxf(m_ref, other.x);
-      const float fa = m_ref == -INFINITY ? 0.0f : ex2((m_ref - m) * scale_log2);
-      const float fb = other.x == -INFINITY ? 0.0f : ex2((other.x - m) * scale_log2);
-      const float l = l_run * fa + other.y * fb;
-      const float inv = l > 0.0f ? 1.0f / l : 0.0f;
-      const float wa = fa * inv, wb = fb * inv;
-      bf16* dst = out + ((size_t)(row0 + row) * nq + h) * D;
-#pragma unroll 1
-      for (int c = 0; c < D; c += 32) {
-        float t[32];
-        tmem_ld32(o_addr + c, t);
-        tmem_wait_ld();
-        if (row < rows) {
+        if (row < rows_q) {
 #pragma unroll
           for (int j = 0; j < 32; j += 8) {
             uint4 v;
             __nv_bfloat162* v2 = reinterpret_cast<__nv_bfloat162*>(&v);
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              const float* o1 = merge_o + row * (D + 1) + c + j + 2 * i;
-              v2[i] = __floats2bfloat162_rn(t[j + 2 * i] * wa + o1[0] * wb, t[j + 2 * i + 1] * wa + o1[1] * wb);
-            }
+            for (int e = 0; e < 4; ++e) v2[e] = __floats2bfloat162_rn(t[j + 2 * e] * inv, t[j + 2 * e + 1] * inv);
             *reinterpret_cast<uint4*>(dst + c + j) = v;
           }
         }
@@ -423,9 +429,9 @@ static int launch_prefill_tcgen05(const bf16* q, int num_tokens, const bf16* kv_
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  return launch_pdl(attn_prefill_tcgen05_kernel<D>, dim3(nq, num_tiles), dim3(kThreads), smem, stream, 1, q_map, pool_map,
-                    block_table, tiles, req_slot, out, nq, nkv, page_size, page_shift, max_blocks, num_pages, window,
-                    scale_log2, error_flag);
+  return launch_pdl(attn_prefill_tcgen05_kernel<D>, dim3(nq, num_tiles), dim3(kThreads), smem, stream, 1, q_map,
+                    pool_map, block_table, tiles, req_slot, out, nq, nkv, page_size, page_shift, max_blocks,
+                    num_pages, window, scale_log2, error_flag);
 }
 
 }  // namespace ifx
@@ -440,7 +446,7 @@ int ifx_attention_prefill_tcgen05_supports(int d, int page_size) {
 }
 
 // q [num_tokens, nq * d] bfloat16, 16-byte aligned.  tiles: int32 [num_tiles, 4] = (request index, first
-// flat row, rows <= 128, first position).
+// flat row, rows <= 256, first position).
 int ifx_attention_prefill_tcgen05(const void* q, int num_tokens, const void* kv_pool, const int* block_table,
                                   const int* tiles, const int* req_slot, void* out, int num_tiles, int nq, int nkv,
                                   int d, int page_size, int max_blocks, int num_pages, int window, float scale,

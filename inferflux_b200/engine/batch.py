@@ -16,7 +16,7 @@ from typing import Dict, Hashable, List, Optional, Sequence
 
 import torch
 
-PREFILL_TILE = 128         # query rows per work item of the prompt-portion attention kernel
+PREFILL_TILE = 256         # query rows per work item of the prompt-portion attention kernel
 
 
 @dataclass

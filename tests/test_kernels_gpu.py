@@ -227,8 +227,8 @@ def make_cache_case(dtype, nkv, d, page, lens, spans, num_pages, seed, shuffle=T
         if s_ == 1:
             decode_rows.append(base)
         else:
-            for off in range(0, s_, 128):
-                tiles.append([r, base + off, min(128, s_ - off), n - s_ + off])
+            for off in range(0, s_, 256):
+                tiles.append([r, base + off, min(256, s_ - off), n - s_ + off])
         base += s_
     ctx.decode_rows = torch.tensor(decode_rows, dtype=torch.int32, device=DEV)
     ctx.decode_meta = torch.tensor([[t, positions[t], slots[token_req[t]], 0] for t in decode_rows],
