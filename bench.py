@@ -281,6 +281,8 @@ def main() -> int:
                          "each, chunked prefill of 512 mixed with decode, through the scheduler")
     ap.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64")
     ap.add_argument("--no-prefill", action="store_true", help="skip the 2,048-token prefill (for profiling decode)")
+    ap.add_argument("--prefill-only", action="store_true",
+                    help="time only the 2,048-token prefill and print a short line (for profiling prefill)")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -316,6 +318,18 @@ def main() -> int:
                           "generated_tokens": gt, "preemptions": pre, "dtype": "bf16", "n_gpus": 1,
                           "config": {"model": f"Qwen2.5-{args.shape.upper()} shape", "prefill_chunk": 512,
                                      "new_tokens": 256, "kv_page": page}, "impl": "ours"}))
+        return 0
+    if args.prefill_only:
+        engine = Engine(config=cfg, seed=0, dtype="bfloat16", device=dev, kv_page_size=page,
+                        kv_num_pages=2 * (PREFILL_TOKENS // page + 2), kv_max_batch=2, kv_max_seq=PREFILL_TOKENS + 64,
+                        max_batch_size=2, max_batch_tokens=8192, chunked_prefill_tokens=PREFILL_TOKENS)
+        ms = time_prefill(engine, cfg, PREFILL_TOKENS, warmup=warmup, reps=steps)
+        frac = prefill_flops(cfg, PREFILL_TOKENS) / (ms * 1e-3) / (pk["bf16_tflops"] * 1e12)
+        print(json.dumps({"metric": "prefill tok/s at 2,048 tokens", "value": round(PREFILL_TOKENS * 1000.0 / ms, 1),
+                          "unit": "tokens/s", "ms": round(ms, 3), "frac": round(frac, 4), "dtype": "bf16", "n_gpus": 1,
+                          "config": {"model": f"Qwen2.5-{args.shape.upper()} shape", "layers": cfg.num_hidden_layers,
+                                     "layers_full": full_layers, "kv_page": page, "peaks": pk["source"]},
+                          "impl": "ours"}))
         return 0
     biggest = max(args.batch, 1 if args.no_points else 64)
     pages = biggest * (CONTEXT // page + 2)
