@@ -15,7 +15,7 @@ ROOT = Path(__file__).resolve().parent.parent
 
 
 def tiny_configs():
-    """Four tiny configurations that differ in every size and option.
+    """Five tiny configurations that differ in every size and option.
     A and B follow the two tiny workloads the benchmark description names; C adds a
     window on its later layers, no biases, and sizes that are no power of two."""
     from inferflux_b200.config import Qwen2Config
@@ -34,7 +34,13 @@ def tiny_configs():
     d = Qwen2Config(hidden_size=100, num_hidden_layers=2, num_attention_heads=3, num_key_value_heads=3,
                     head_dim=24, intermediate_size=150, vocab_size=333, max_position_embeddings=300,
                     rope_theta=20000.0, rms_norm_eps=1e-5, tie_word_embeddings=True)
-    return {"A": (a, 4), "B": (b, 8), "C": (c, 16), "D": (d, 16)}
+    # E: head size 64 and pages of 16, the sizes the tensor-core prompt attention takes; a window on
+    # its second layer that ends inside the 128-key tiles.
+    e = Qwen2Config(hidden_size=136, num_hidden_layers=2, num_attention_heads=6, num_key_value_heads=2,
+                    head_dim=64, intermediate_size=264, vocab_size=640, max_position_embeddings=512,
+                    rope_theta=300000.0, rms_norm_eps=2e-6, tie_word_embeddings=False,
+                    use_sliding_window=True, sliding_window=150, max_window_layers=1)
+    return {"A": (a, 4), "B": (b, 8), "C": (c, 16), "D": (d, 16), "E": (e, 16)}
 
 
 def write_tiny_model(cfg, out_dir, seed, dtype=torch.float32):

@@ -74,6 +74,34 @@ def test_step_function_cuttings(name, dtype, cutting, model_dirs, tiny_configs, 
         assert g0["free"] == g0["pages"]
 
 
+LENS_E = [300, 150, 40, 260, 70, 385]
+MAX_TOKENS_E = 832
+
+
+@pytest.mark.parametrize("dtype", ["bfloat16", "float32"])
+@pytest.mark.parametrize("cutting", ["whole", "tail", "portions", "mixed"])
+def test_long_requests_through_the_tensor_core_attention(dtype, cutting, model_dirs, tiny_configs, cuda_kernels):
+    """Configuration E (head size 64, pages of 16) with requests of several hundred tokens: prompt
+    portions of more than one 128-row query tile over several 128-key tiles, behind a cached prefix,
+    with a window on the second layer, cut in every way."""
+    cfg, page = tiny_configs["E"]
+    d, _ = model_dirs["E"]
+    assert cuda_kernels.tensor_core_prefill and cuda_kernels.lib.ifx_attention_prefill_tcgen05_supports(cfg.head_dim, page)
+    reqs = {f"e{i}": helpers.random_tokens(cfg.vocab_size, n, 300 + i) for i, n in enumerate(LENS_E)}
+    want = helpers.plain_logits(d, reqs, weights_as=torch.bfloat16 if dtype == "bfloat16" else None)
+    steps = {"whole": helpers.trace_whole, "tail": helpers.trace_tail, "portions": helpers.trace_portions,
+             "mixed": lambda r: helpers.trace_mixed(r, MAX_TOKENS_E)}[cutting](reqs)
+    runner = make_runner(d, page, dtype, cuda_kernels, max_tokens=MAX_TOKENS_E)
+    before = cuda_kernels.launches
+    got = helpers.collect(steps, helpers.run_steps_in_process(runner, steps), cfg.vocab_size)
+    check(got, want, dtype, f"E/{dtype}/{cutting}")
+    cuda_kernels.check_errors()
+    assert cuda_kernels.launches > before and not runner.cache.live_requests()
+    if cutting == "mixed":
+        g0 = runner.cache.stats()["groups"][0]
+        assert g0["allocations"] > g0["pages"], "the pool was large enough that no page was used again"
+
+
 @pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_float32_is_the_same_under_every_cutting(name, model_dirs, tiny_configs, cuda_kernels):
     """The 32-bit kernels add in an order that depends on the position only, so
