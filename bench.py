@@ -167,7 +167,7 @@ def time_decode(engine, cfg, batch, steps, warmup, sampler_clock=None):
     total = warmup + steps
     prompt_len = CONTEXT - 2 * total - 2
     prompts = random_prompts(cfg, batch, prompt_len, seed=batch)
-    bring_to_decode(engine, prompts, max_tokens=4 * total + 8)
+    bring_to_decode(engine, prompts, max_tokens=4 * total + 8 + batch)   # the first ones decode while the last prefill
     runner, kernels = engine.runner, engine.kernels
 
     # ---- end to end through the entry point: scheduler, step, sampling, ids back to the host
