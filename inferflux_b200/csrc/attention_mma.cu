@@ -786,9 +786,9 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap pool_map, const bf16*
   const int DS = D / num_splits;
   for (int idx = tid; idx < G * DS; idx += 128) {
     const int row = idx / DS, dim = split * DS + idx % DS;
-    float ms[8], ls[8], os[8];
+    float ms[16], ls[16], os[16];
 #pragma unroll
-    for (int c = 0; c < 8; ++c) {
+    for (int c = 0; c < 16; ++c) {
       if (c < num_splits) {
         ms[c] = cluster.map_shared_rank(fin_m, c)[row];
         ls[c] = cluster.map_shared_rank(fin_l, c)[row];
@@ -800,11 +800,11 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap pool_map, const bf16*
     }
     float M = -INFINITY;
 #pragma unroll
-    for (int c = 0; c < 8; ++c) M = fmaxf(M, ms[c]);
+    for (int c = 0; c < 16; ++c) M = fmaxf(M, ms[c]);
     float O = 0.0f, L = 0.0f;
     if (M != -INFINITY) {
 #pragma unroll
-      for (int c = 0; c < 8; ++c) {
+      for (int c = 0; c < 16; ++c) {
         const float f = exp2f(ms[c] - M);
         O += f * os[c];
         L += f * ls[c];
@@ -835,6 +835,15 @@ int launch_decode_tma(const CUtensorMap& pool_map, const bf16* q, const int* blo
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return (int)e;
     configured = smem;
+  }
+  if (num_splits > 8) {                                   // a cluster of 16 is beyond the portable size
+    static bool allowed = false;
+    if (!allowed) {
+      cudaError_t e = cudaFuncSetAttribute(attn_decode_tma_kernel<D, STAGES>,
+                                           cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+      if (e != cudaSuccess) return (int)e;
+      allowed = true;
+    }
   }
   return launch_pdl(attn_decode_tma_kernel<D, STAGES>, dim3(num_items, nkv, num_splits), dim3(128), (size_t)smem, stream,
                     num_splits, pool_map, q, block_table, decode_meta, out, nq, nkv, page_size, page_shift, max_blocks,
@@ -951,9 +960,16 @@ int ifx_attention_prefill_bf16(const void* q, const void* kv_pool, const int* bl
 #undef CALL
 }
 
+// The largest cluster (blocks that share one token's keys) the decode kernel takes for this head and page size.
+int ifx_attention_decode_max_splits(int d, int page_size) {
+  const int ps = shift_of(page_size);
+  return (ps >= 4 && (d == 64 || d == 128)) ? 16 : 8;
+}
+
 // decode_meta: int32 [num_items, 4] = (flat token row, position, request slot, unused).
 // error_flag: device int that the TMA variant sets if a bounded wait runs out (nullptr: cp.async variant only).
-// num_splits: 1, 2, 4 or 8 blocks (one cluster) share a token's key range; it must divide d.
+// num_splits: 1, 2, 4 or 8 blocks (one cluster) share a token's key range; it must divide d.  16 where
+// ifx_attention_decode_max_splits says so (the TMA variant, a cluster size beyond the portable 8).
 // max_keys: no token of the step sees more keys than this.
 int ifx_attention_decode_bf16(const void* q, const void* kv_pool, const int* block_table, const int* decode_meta,
                               void* out, int num_items, int nq, int nkv, int d, int page_size, int max_blocks,
@@ -963,11 +979,13 @@ int ifx_attention_decode_bf16(const void* q, const void* kv_pool, const int* blo
   if (nq <= 0 || nkv <= 0 || nq % nkv || nq / nkv > 16 || page_size <= 0 || max_blocks <= 0 || nkv > 65535 ||
       nq > 65535)
     return IFX_E_BADARG;
-  if (!(num_splits == 1 || num_splits == 2 || num_splits == 4 || num_splits == 8) || d % num_splits)
+  const int ps = shift_of(page_size);
+  const bool tma = ps >= 4 && d % 64 == 0 && error_flag != nullptr;
+  if (!(num_splits == 1 || num_splits == 2 || num_splits == 4 || num_splits == 8 || (num_splits == 16 && tma)) ||
+      d % num_splits)
     return IFX_E_BADARG;
   const float scale_log2 = scale * 1.4426950408889634f;
-  const int ps = shift_of(page_size);
-  if (ps >= 4 && d % 64 == 0 && error_flag != nullptr) {       // pages of 16, 32, ... tokens: the TMA kernel
+  if (tma) {                                                    // pages of 16, 32, ... tokens: the TMA kernel
     CUtensorMap pool_map;
     const long long rows = (long long)num_pages * 2 * nkv * page_size;
     int rc = pool_tensor_map(&pool_map, kv_pool, rows, d);

@@ -100,7 +100,7 @@ class CudaKernels:
                    "ifx_scatter_i32", "ifx_rope_append", "ifx_attention_generic", "ifx_gemm_generic",
                    "ifx_gemm_cublas_bf16", "ifx_cublas_init", "ifx_argmax", "ifx_penalties", "ifx_logit_bias",
                    "ifx_sample", "ifx_attention_mma_supports", "ifx_attention_prefill_bf16",
-                   "ifx_attention_prefill_tcgen05", "ifx_attention_prefill_tcgen05_supports",
+                   "ifx_attention_prefill_tcgen05", "ifx_attention_prefill_tcgen05_supports", "ifx_attention_decode_max_splits",
                    "ifx_attention_decode_bf16", "ifx_gemm_skinny", "ifx_residual_add_partial",
                    "ifx_reduce_partial", "ifx_reduce_add_rmsnorm", "ifx_argmax_chunks", "ifx_relay_i32", "ifx_prenorm", "ifx_scale_rows"):
             getattr(self.lib, fn).restype = ctypes.c_int
@@ -406,7 +406,7 @@ class CudaKernels:
                 self._attention_generic(q, kv, table, ctx, ctx.decode_rows, n, out, nq, nkv, d, common)
                 return out
             max_keys = int(ctx.max_kv_len if not win else min(win, ctx.max_kv_len))
-            splits = self.decode_splits(n, nkv, max_keys)
+            splits = self.decode_splits(n, nkv, max_keys, int(self.lib.ifx_attention_decode_max_splits(d, cache.page_size)))
             _check(self.lib.ifx_attention_decode_bf16(
                 _ptr(q), _ptr(kv), _ptr(table), _ptr(ctx.decode_meta), _ptr(out), n, nq, nkv, d, *common, splits,
                 max_keys, _ptr(self.error_flag), _stream()), "attention (decoded tokens)")
@@ -414,11 +414,12 @@ class CudaKernels:
         return out
 
     @staticmethod
-    def decode_splits(num_tokens, nkv, max_keys):
-        """Into how many thread blocks (one cluster: 1, 2, 4 or 8) the key range of a decoded
-        token is cut: enough blocks to fill the 148 SMs twice, but at least 128 keys per block."""
+    def decode_splits(num_tokens, nkv, max_keys, max_splits=8):
+        """Into how many thread blocks (one cluster: 1, 2, 4, 8, or 16 where the kernel takes it) the
+        key range of a decoded token is cut: enough blocks to fill the 148 SMs twice, but at least
+        128 keys per block."""
         want = -(-296 // max(1, num_tokens * nkv))
-        limit = max(1, min(want, max_keys // 128, 8))
+        limit = max(1, min(want, max_keys // 128, max_splits))
         splits = 1
         while splits * 2 <= limit:
             splits *= 2

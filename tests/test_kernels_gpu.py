@@ -303,6 +303,32 @@ def test_attention_over_pages(cuda_kernels, dtype, nq, nkv, d, page, window):
     close(got.cpu(), want, atol=2e-5 if dtype == torch.float32 else 2e-2, rtol=1e-5 if dtype == torch.float32 else 2e-2)
 
 
+@pytest.mark.parametrize("nq,nkv,d,page,window", [(14, 2, 128, 16, None), (4, 1, 64, 32, None), (8, 2, 128, 16, 2300)])
+def test_attention_decode_one_token_over_a_cluster_of_sixteen(cuda_kernels, nq, nkv, d, page, window):
+    """One or two decoded tokens with thousands of keys: the key range is cut over the largest
+    cluster the kernel takes, and the planted key may lie in any block of it."""
+    dtype = torch.bfloat16
+    lens, spans = [2600, 2333], [1, 1]
+    assert cuda_kernels.decode_splits(2, nkv, 2333, cuda_kernels.lib.ifx_attention_decode_max_splits(d, page)) == 16
+    for target_of in (lambda first, pos: first, lambda first, pos: pos, lambda first, pos: first + (pos - first) * 5 // 16,
+                      lambda first, pos: first + (pos - first) * 15 // 16):
+        ctx, cache, slots = make_cache_case(dtype, nkv, d, page, lens, spans,
+                                            num_pages=sum(-(-n // page) for n in lens) + 3, seed=23)
+        stored = fill_cache(cache, lens, slots, nkv, d, dtype, seed=24)
+        q = rnd(2, nq, d, dtype=dtype, seed=25, scale=0.3)
+        for t, n in enumerate(lens):
+            pos = n - 1
+            first = max(0, pos - window + 1) if window else 0
+            for h in range(nq):
+                g = h // (nq // nkv)
+                q[t, h] = (stored[t][0][target_of(first, pos), g].float() * (12.0 / math.sqrt(d))).to(dtype).to(DEV)
+        scale = 1.0 / math.sqrt(d)
+        want = attention_oracle(q, stored, lens, spans, nq, nkv, d, window, scale)
+        got = cuda_kernels.attention(q.view(2, nq * d), nq, nkv, d, window, scale, ctx, cache)
+        close(got.cpu(), want, atol=2e-2, rtol=2e-2)
+    cuda_kernels.check_errors()
+
+
 @pytest.mark.parametrize("nq,nkv,d,page,window", [
     (4, 2, 128, 16, None), (6, 1, 64, 16, None), (4, 4, 128, 32, 200), (3, 1, 64, 64, 129), (2, 1, 96, 16, 300)])
 def test_attention_long_portions(cuda_kernels, nq, nkv, d, page, window):
