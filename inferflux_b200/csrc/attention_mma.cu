@@ -577,7 +577,9 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap pool_map, const bf16*
     for (int i = 0; i < 4 * STAGES; ++i) mbar_init(smem_addr(bars + i), 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  pdl_wait();                                           // the queries, the cache and the tables are the step's own
+  // The step's metadata, the block table and every key but the token's own were written before this
+  // step's kernels began: tables are copied and the first tiles are on their way before the kernel in
+  // front (which writes the token's own key and value, and the queries) is known to have finished.
   const int4 meta = decode_meta[item];
   const int t = meta.x;
   const int pos = meta.y;
@@ -599,19 +601,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap pool_map, const bf16*
       blk_base = b0;
     }
   }
-  for (int i = tid; i < 16 * CPR; i += 128) {
-    const int row = i / CPR, c = i % CPR;
-    uint4 v = make_uint4(0u, 0u, 0u, 0u);
-    if (row < G) v = *reinterpret_cast<const uint4*>(q + ((size_t)t * nq + g * G + row) * D + c * 8);
-    *reinterpret_cast<uint4*>(q_s + row * LDS + c * 8) = v;
-  }
-  __syncthreads();
-  uint32_t qf[D / 16][4];
-#pragma unroll
-  for (int kk = 0; kk < D / 16; ++kk) {
-    const int row = (lane & 7) + ((lane >> 3) & 1) * 8, col = kk * 16 + (lane >> 4) * 8;
-    ldmatrix_x4(qf[kk], smem_u32(q_s + row * LDS + col));
-  }
+  __syncthreads();                                      // barriers initialised, table copied
 
   const uint32_t my_stage0 = smem_addr(stage_base) + warp * STAGES * STAGE_BYTES;
   const uint32_t my_bar0 = smem_addr(bars + warp * STAGES);
@@ -634,18 +624,42 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap pool_map, const bf16*
     return (uint32_t)((col >> 6) * 2048 + row * 128 + ((((col & 63) >> 3) ^ (row & 7)) << 4));
   };
 
+  const int first_base = k0 + warp * 16;
+  const int stride = 64;
+  if (lane == 0) {
+#pragma unroll
+    for (int s = 0; s < STAGES - 1; ++s) {
+      const int base = first_base + s * stride;
+      if (base < k1 && base + 16 <= pos) issue_tile(base, s);       // the tile with the token's own key waits
+    }
+  }
+  pdl_wait();
+  if (lane == 0) {
+#pragma unroll
+    for (int s = 0; s < STAGES - 1; ++s) {
+      const int base = first_base + s * stride;
+      if (base < k1 && base + 16 > pos) issue_tile(base, s);
+    }
+  }
+  for (int i = tid; i < 16 * CPR; i += 128) {
+    const int row = i / CPR, c = i % CPR;
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (row < G) v = *reinterpret_cast<const uint4*>(q + ((size_t)t * nq + g * G + row) * D + c * 8);
+    *reinterpret_cast<uint4*>(q_s + row * LDS + c * 8) = v;
+  }
+  __syncthreads();
+  uint32_t qf[D / 16][4];
+#pragma unroll
+  for (int kk = 0; kk < D / 16; ++kk) {
+    const int row = (lane & 7) + ((lane >> 3) & 1) * 8, col = kk * 16 + (lane >> 4) * 8;
+    ldmatrix_x4(qf[kk], smem_u32(q_s + row * LDS + col));
+  }
+
   float o[D / 8][4];
 #pragma unroll
   for (int i = 0; i < D / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
   float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.0f, l_hi = 0.0f;
 
-  const int first_base = k0 + warp * 16;
-  const int stride = 64;
-  if (lane == 0) {
-#pragma unroll
-    for (int s = 0; s < STAGES - 1; ++s)
-      if (first_base + s * stride < k1) issue_tile(first_base + s * stride, s);
-  }
   int n_iter = 0;
   bool ok = true;
   for (int base = first_base; base < k1; base += stride, ++n_iter) {
