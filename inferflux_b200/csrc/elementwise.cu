@@ -198,15 +198,17 @@ prenorm_kernel(float* __restrict__ x, const void* __restrict__ delta_raw, const 
                int chunks) {
   __shared__ float scratch[32];
   pdl_launch_dependents();
-  pdl_wait();
   const int row = blockIdx.x, chunk = blockIdx.y;
   float* xr = x + (size_t)row * hidden;
   T* pr = pre + (size_t)row * hidden;
   const int c0 = chunk * kNormChunk + threadIdx.x * 4;
+  const bool wide = c0 + 3 < hidden && (hidden & 3) == 0;
+  float4 wv = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (wide) wv = *reinterpret_cast<const float4*>(w + c0);         // the norm's weight is nobody's output
+  pdl_wait();
   float ss = 0.0f;
-  if (c0 + 3 < hidden && (hidden & 3) == 0) {
+  if (wide) {
     float4 v = *reinterpret_cast<const float4*>(xr + c0);
-    const float4 wv = *reinterpret_cast<const float4*>(w + c0);
     if (MODE == 1) {
       const T* d = reinterpret_cast<const T*>(delta_raw) + (size_t)row * hidden + c0;
       v.x += to_f32(d[0]); v.y += to_f32(d[1]); v.z += to_f32(d[2]); v.w += to_f32(d[3]);

@@ -24,7 +24,8 @@ __global__ void rope_append_kernel(const T* __restrict__ qkv, const float* __res
                                    int max_blocks, int page_size, int num_pages, T* __restrict__ kv_pool,
                                    T* __restrict__ q_out, int nq, int nkv, int d, int write_cache) {
   pdl_launch_dependents();
-  pdl_wait();
+  // Positions, slots, the block table, the bias and the angles do not come from the kernel in front:
+  // they are fetched and the sines computed before it is known to have finished.
   const int t = blockIdx.x;
   const int head = blockIdx.y;                      // [0, nq) q, [nq, nq+nkv) k, then v
   const int width = (nq + 2 * nkv) * d;
@@ -40,43 +41,53 @@ __global__ void rope_append_kernel(const T* __restrict__ qkv, const float* __res
   const float* b = bias ? bias + (size_t)head * d : nullptr;
   const int pos = positions[t];
 
-  T* dst;
-  bool rotate;
+  T* dst = nullptr;
+  bool rotate = true;
   if (head < nq) {
     dst = q_out + (size_t)t * nq * d + (size_t)head * d;
-    rotate = true;
-  } else {
-    if (!write_cache) return;
+  } else if (write_cache) {
     const int is_v = head >= nq + nkv;
     const int g = head - nq - (is_v ? nkv : 0);
     const int slot = req_slot[token_req[t]];
     const int page = block_table[(size_t)slot * max_blocks + pos / page_size];
-    if (page < 0 || page >= num_pages) return;      // never write outside the pool
-    dst = kv_pool + ((((size_t)page * 2 + is_v) * nkv + g) * page_size + (pos % page_size)) * d;
+    if (page >= 0 && page < num_pages)              // never write outside the pool
+      dst = kv_pool + ((((size_t)page * 2 + is_v) * nkv + g) * page_size + (pos % page_size)) * d;
     rotate = !is_v;
   }
 
   const int half_rot = rot / 2;
-  for (int j = threadIdx.x; j < d / 2; j += blockDim.x) {
+  struct Pair {
     int e0, e1;
-    bool turn = rotate && j < half_rot;
+    bool turn;
+    float sn, cs, b0, b1;
+  };
+  auto prepare = [&](int j) -> Pair {
+    Pair p;
+    p.turn = rotate && j < half_rot;
     if (j < half_rot) {
-      e0 = interleaved ? 2 * j : j;
-      e1 = interleaved ? 2 * j + 1 : j + half_rot;
+      p.e0 = interleaved ? 2 * j : j;
+      p.e1 = interleaved ? 2 * j + 1 : j + half_rot;
     } else {
-      e0 = rot + 2 * (j - half_rot);
-      e1 = e0 + 1;
+      p.e0 = rot + 2 * (j - half_rot);
+      p.e1 = p.e0 + 1;
     }
-    float a = load(e0), c = load(e1);
-    if (b) {
-      a += b[e0];
-      c += b[e1];
-    }
-    if (turn) {
-      float sn, cs;
-      sincosf((float)pos * inv_freq[j], &sn, &cs);
-      const float ra = a * cs - c * sn;
-      const float rc = a * sn + c * cs;
+    p.b0 = b ? b[p.e0] : 0.0f;
+    p.b1 = b ? b[p.e1] : 0.0f;
+    p.sn = 0.0f;
+    p.cs = 1.0f;
+    if (p.turn) sincosf((float)pos * inv_freq[j], &p.sn, &p.cs);
+    return p;
+  };
+  Pair first = {};
+  if ((int)threadIdx.x < d / 2) first = prepare(threadIdx.x);
+  pdl_wait();
+  if (dst == nullptr) return;
+  for (int j = threadIdx.x; j < d / 2; j += blockDim.x) {
+    const Pair p = j == (int)threadIdx.x ? first : prepare(j);
+    float a = load(p.e0) + p.b0, c = load(p.e1) + p.b1;
+    if (p.turn) {
+      const float ra = a * p.cs - c * p.sn;
+      const float rc = a * p.sn + c * p.cs;
       a = ra;
       c = rc;
     }
@@ -84,8 +95,8 @@ __global__ void rope_append_kernel(const T* __restrict__ qkv, const float* __res
       a = isfinite(a) ? a : 0.0f;     // weight zero, and zero times it must be zero whoever wrote it
       c = isfinite(c) ? c : 0.0f;
     }
-    dst[e0] = from_f32<T>(a);
-    dst[e1] = from_f32<T>(c);
+    dst[p.e0] = from_f32<T>(a);
+    dst[p.e1] = from_f32<T>(c);
   }
 }
 
