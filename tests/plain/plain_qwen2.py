@@ -83,7 +83,7 @@ def layer_window(cfg, layer):
 def embedding(table, tokens):
     """x0[t,:] = E[token[t],:], no scaling
     (runtime/backends/cuda/native/cuda_kernels.cu:256-270)."""
-    return table[tokens.long()]
+    return table[tokens.long().to(table.device)]
 
 
 def rmsnorm(x, w, eps):
@@ -109,7 +109,7 @@ def rope_neox(x, positions, theta):
     d = x.shape[-1]
     half = d // 2
     inv_freq = 1.0 / (theta ** (torch.arange(0, d, 2, dtype=torch.float32) / d))
-    ang = positions.to(torch.float32)[:, None] * inv_freq[None, :]          # fp32 angles
+    ang = (positions.to(torch.float32)[:, None] * inv_freq[None, :]).to(x.device)   # fp32 angles, made on the CPU
     cos = torch.cos(ang).to(x.dtype)[:, None, :]
     sin = torch.sin(ang).to(x.dtype)[:, None, :]
     a, b = x[..., :half], x[..., half:]
@@ -126,7 +126,7 @@ def attention_gqa_causal(q, k, v, window=None):
     group = nq // nkv
     scale = 1.0 / math.sqrt(d)
     out = torch.zeros_like(q)
-    idx = torch.arange(T)
+    idx = torch.arange(T, device=q.device)
     seen = idx[None, :] <= idx[:, None]
     if window is not None:
         seen &= idx[None, :] > (idx[:, None] - window)

@@ -1,0 +1,78 @@
+"""The three real layer shapes (Qwen2.5-1.5B, -7B, -32B: every size of a layer, of the
+embedding and of the head as the models have them) with one layer and random weights:
+the 32-bit path against the plain implementation under two cuttings, and the bfloat16
+path against the same oracle with the tolerance its roundings need.
+
+The plain implementation runs on the GPU here (float64, the same functions as on the
+CPU) because of the size of the vocabulary; weights are made on the device by the
+framework's seeded generator, so both sides draw the same values without a file.
+"""
+import numpy as np
+import pytest
+import torch
+
+import helpers
+
+pytestmark = pytest.mark.gpu
+
+SHAPES = {
+    "1.5b": dict(hidden_size=1536, num_attention_heads=12, num_key_value_heads=2, head_dim=128, intermediate_size=8960,
+                 vocab_size=151936, rope_theta=1000000.0, rms_norm_eps=1e-6, tie_word_embeddings=True),
+    "7b": dict(hidden_size=3584, num_attention_heads=28, num_key_value_heads=4, head_dim=128, intermediate_size=18944,
+               vocab_size=152064, rope_theta=1000000.0, rms_norm_eps=1e-6, tie_word_embeddings=False),
+    "32b": dict(hidden_size=5120, num_attention_heads=40, num_key_value_heads=8, head_dim=128, intermediate_size=27648,
+                vocab_size=152064, rope_theta=1000000.0, rms_norm_eps=1e-5, tie_word_embeddings=False),
+}
+LENS = [70, 37]
+
+
+def make(shape, dtype, cuda_kernels):
+    from inferflux_b200.config import Qwen2Config
+    from inferflux_b200.engine import ModelRunner
+    from inferflux_b200.models import random_model
+    cfg = Qwen2Config(num_hidden_layers=1, max_position_embeddings=512, **SHAPES[shape])
+    model = random_model(cfg, seed=5, dtype=dtype, device="cuda:0", norm_jitter=0.2)
+    return cfg, model, ModelRunner(model, cuda_kernels, page_size=16, num_pages=16, max_seqs=4)
+
+
+def oracle(cfg, model, reqs, weights_as):
+    from inferflux_b200.weights import random_tensors
+    from plain import plain_qwen2
+    store = torch.float32 if weights_as is None else weights_as
+    W = random_tensors(model.expected_tensors(), 5, dtype=store, device="cuda:0", norm_jitter=0.2)
+    if cfg.tie_word_embeddings:
+        W.pop("lm_head.weight", None)
+    raw = cfg.to_dict()
+    out = {rid: plain_qwen2.forward(raw, W, toks, dtype=torch.float64).cpu().numpy() for rid, toks in reqs.items()}
+    del W
+    torch.cuda.empty_cache()
+    return out
+
+
+@pytest.mark.parametrize("shape", ["1.5b", "7b", "32b"])
+def test_real_layer_shapes_in_32_bit(shape, cuda_kernels):
+    cfg, model, runner = make(shape, "float32", cuda_kernels)
+    reqs = {f"r{i}": helpers.random_tokens(cfg.vocab_size, n, 700 + i) for i, n in enumerate(LENS)}
+    want = oracle(cfg, model, reqs, None)
+    for make_trace in (helpers.trace_whole, helpers.trace_portions, lambda r: helpers.trace_mixed(r, 256)):
+        steps = make_trace(reqs)
+        got = helpers.collect(steps, helpers.run_steps_in_process(runner, steps), cfg.vocab_size)
+        bad = helpers.first_bad(got, want, 1e-4)
+        assert bad is None, f"{shape}: first wrong row (request, position, diff) = {bad}"
+        assert not runner.cache.live_requests()
+
+
+@pytest.mark.parametrize("shape", ["1.5b", "7b", "32b"])
+def test_real_layer_shapes_in_bfloat16(shape, cuda_kernels):
+    cfg, model, runner = make(shape, "bfloat16", cuda_kernels)
+    reqs = {f"r{i}": helpers.random_tokens(cfg.vocab_size, n, 700 + i) for i, n in enumerate(LENS)}
+    want = oracle(cfg, model, reqs, torch.bfloat16)
+    scale = max(float(np.abs(w).max()) for w in want.values())
+    for make_trace in (helpers.trace_whole, helpers.trace_tail, lambda r: helpers.trace_mixed(r, 256)):
+        steps = make_trace(reqs)
+        got = helpers.collect(steps, helpers.run_steps_in_process(runner, steps), cfg.vocab_size)
+        bad = helpers.first_bad(got, want, 0.03 * scale)
+        assert bad is None, f"{shape}: first wrong row (request, position, diff) = {bad}, scale {scale}"
+        agree = np.mean([np.mean(got[r].argmax(-1) == want[r].argmax(-1)) for r in want])
+        assert agree > 0.9, f"{shape}: the best token agrees at only {agree:.2f} of the positions"
+    cuda_kernels.check_errors()
