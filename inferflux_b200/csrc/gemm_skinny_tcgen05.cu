@@ -222,7 +222,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
           float v = __uint_as_float(g[j]) * rs;
           if (MODE == MODE_SWIGLU) {
             const float up = __uint_as_float(u[j]) * rs;
-            v = v / (1.0f + expf(-v)) * up;
+            v = __fdividef(v, 1.0f + __expf(-v)) * up;       // a few float32 ulps, far below the bfloat16 rounding
           }
           if (MODE == MODE_PARTIAL) {
             partials[((size_t)split * M + m) * N + n] = v;
