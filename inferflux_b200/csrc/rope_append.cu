@@ -106,7 +106,7 @@ __global__ void rope_append_kernel(const T* __restrict__ qkv, const float* __res
 // its rotation partner half a head away) per step.  Takes the common case only:
 // bfloat16 activations (not partial sums), whole-head split-half rotation, head
 // sizes that are multiples of 16.
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(1024)
 rope_append_rows_kernel(const __nv_bfloat16* __restrict__ qkv, const float* __restrict__ bias,
                         const float* __restrict__ inv_freq, const int* __restrict__ positions,
                         const int* __restrict__ token_req, const int* __restrict__ req_slot,
@@ -115,8 +115,21 @@ rope_append_rows_kernel(const __nv_bfloat16* __restrict__ qkv, const float* __re
                         int write_cache) {
   __shared__ float cs[128], sn[128];                    // d / 2 <= 128
   const int t = blockIdx.x;
-  const int pos = positions[t];
   const int half = d / 2;
+  const int width = (nq + 2 * nkv) * d;
+  const int cph = half / 8;                             // 16-byte chunks per half head
+  const int items = (nq + 2 * nkv) * cph;
+  const __nv_bfloat16* row = qkv + (size_t)t * width;
+  // The block has one thread per item where it can; the item's loads go out before the chain
+  // position -> angles and token -> slot -> page is followed.
+  int it = threadIdx.x;
+  uint4 lo_raw = make_uint4(0u, 0u, 0u, 0u), hi_raw = lo_raw;
+  if (it < items) {
+    const int head = it / cph, c = (it % cph) * 8;
+    lo_raw = *reinterpret_cast<const uint4*>(row + head * d + c);
+    hi_raw = *reinterpret_cast<const uint4*>(row + head * d + half + c);
+  }
+  const int pos = positions[t];
   for (int j = threadIdx.x; j < half; j += blockDim.x) sincosf((float)pos * inv_freq[j], &sn[j], &cs[j]);
   size_t page_base = 0;
   bool page_ok = false;
@@ -127,12 +140,12 @@ rope_append_rows_kernel(const __nv_bfloat16* __restrict__ qkv, const float* __re
     page_base = (size_t)page * 2 * nkv * page_size * d + (size_t)(pos % page_size) * d;
   }
   __syncthreads();
-  const int width = (nq + 2 * nkv) * d;
-  const int cph = half / 8;                             // 16-byte chunks per half head
-  const int items = (nq + 2 * nkv) * cph;
-  const __nv_bfloat16* row = qkv + (size_t)t * width;
-  for (int it = threadIdx.x; it < items; it += blockDim.x) {
+  for (; it < items; it += blockDim.x) {
     const int head = it / cph, c = (it % cph) * 8;
+    if (it != (int)threadIdx.x) {                        // more items than threads: the later ones load here
+      lo_raw = *reinterpret_cast<const uint4*>(row + head * d + c);
+      hi_raw = *reinterpret_cast<const uint4*>(row + head * d + half + c);
+    }
     const bool is_q = head < nq, is_v = head >= nq + nkv;
     __nv_bfloat16* dst;
     if (is_q) {
@@ -142,8 +155,15 @@ rope_append_rows_kernel(const __nv_bfloat16* __restrict__ qkv, const float* __re
       const int g = head - nq - (is_v ? nkv : 0);
       dst = kv_pool + page_base + ((size_t)(is_v ? nkv : 0) + g) * page_size * d;
     }
-    const uint4 lo_raw = *reinterpret_cast<const uint4*>(row + head * d + c);
-    const uint4 hi_raw = *reinterpret_cast<const uint4*>(row + head * d + half + c);
+    float blo[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f}, bhi[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    if (bias) {                                          // d % 16 == 0: both runs of 8 floats are 32-byte aligned
+      const float4* bl = reinterpret_cast<const float4*>(bias + head * d + c);
+      const float4* bh = reinterpret_cast<const float4*>(bias + head * d + half + c);
+      *reinterpret_cast<float4*>(blo) = bl[0];
+      *reinterpret_cast<float4*>(blo + 4) = bl[1];
+      *reinterpret_cast<float4*>(bhi) = bh[0];
+      *reinterpret_cast<float4*>(bhi + 4) = bh[1];
+    }
     const __nv_bfloat162* lo2 = reinterpret_cast<const __nv_bfloat162*>(&lo_raw);
     const __nv_bfloat162* hi2 = reinterpret_cast<const __nv_bfloat162*>(&hi_raw);
     uint4 lo_out, hi_out;
@@ -152,12 +172,10 @@ rope_append_rows_kernel(const __nv_bfloat16* __restrict__ qkv, const float* __re
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
       float2 a = __bfloat1622float2(lo2[k]), b = __bfloat1622float2(hi2[k]);
-      if (bias) {
-        a.x += bias[head * d + c + 2 * k];
-        a.y += bias[head * d + c + 2 * k + 1];
-        b.x += bias[head * d + half + c + 2 * k];
-        b.y += bias[head * d + half + c + 2 * k + 1];
-      }
+      a.x += blo[2 * k];
+      a.y += blo[2 * k + 1];
+      b.x += bhi[2 * k];
+      b.y += bhi[2 * k + 1];
       if (!is_v) {
         const float c0 = cs[c + 2 * k], s0 = sn[c + 2 * k], c1 = cs[c + 2 * k + 1], s1 = sn[c + 2 * k + 1];
         const float ax = a.x * c0 - b.x * s0, bx = a.x * s0 + b.x * c0;
@@ -198,8 +216,11 @@ extern "C" int ifx_rope_append(const void* qkv, const float* qkv_partial, int nu
   const size_t split_stride = (size_t)num_tokens * (nq + 2 * nkv) * d;
   if (dtype == IFX_DT_BF16 && qkv != nullptr && num_tokens >= 64 && rot == d && !interleaved && d % 16 == 0 &&
       d <= 256 && (reinterpret_cast<uintptr_t>(qkv) % 16 == 0) && (reinterpret_cast<uintptr_t>(q_out) % 16 == 0) &&
-      (kv_pool == nullptr || reinterpret_cast<uintptr_t>(kv_pool) % 16 == 0)) {
-    rope_append_rows_kernel<<<num_tokens, 256, 0, stream>>>(
+      (kv_pool == nullptr || reinterpret_cast<uintptr_t>(kv_pool) % 16 == 0) &&
+      (bias == nullptr || reinterpret_cast<uintptr_t>(bias) % 16 == 0)) {
+    const int items = (nq + 2 * nkv) * (d / 16);
+    const int threads = items >= 1024 ? 1024 : (items + 31) / 32 * 32;
+    rope_append_rows_kernel<<<num_tokens, threads, 0, stream>>>(
         (const __nv_bfloat16*)qkv, bias, inv_freq, positions, token_req, req_slot, block_table, max_blocks, page_size,
         num_pages, (__nv_bfloat16*)kv_pool, (__nv_bfloat16*)q_out, nq, nkv, d, write_cache);
     IFX_CHECK_LAUNCH();
