@@ -244,14 +244,14 @@ def time_prefill(engine, cfg, tokens, warmup, reps):
     return statistics.median(times)
 
 
-def serve_workload(engine, cfg, requests, new_tokens, seed=3):
+def serve_workload(engine, cfg, requests, new_tokens, seed=3, prompt_len=0):
     """Many requests with prompts of uniform random length through the scheduler: chunked
     prefill mixed with decode, as a server would run them.  Returns (seconds, prompt tokens,
     generated tokens, steps, preemptions)."""
     import torch
     from inferflux_b200.sampling import SamplingParams
     g = torch.Generator().manual_seed(seed)
-    lens = torch.randint(128, 2049, (requests,), generator=g).tolist()
+    lens = [prompt_len] * requests if prompt_len else torch.randint(128, 2049, (requests,), generator=g).tolist()
     prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in lens]
     for p in prompts:
         engine.add_request(p, SamplingParams(temperature=0.0), max_tokens=new_tokens)
@@ -279,6 +279,9 @@ def main() -> int:
     ap.add_argument("--serve", type=int, default=0, metavar="REQUESTS",
                     help="instead of the decode/prefill numbers: REQUESTS prompts of 128..2048 tokens, 256 new tokens "
                          "each, chunked prefill of 512 mixed with decode, through the scheduler")
+    ap.add_argument("--serve-prompt", type=int, default=0, metavar="TOKENS",
+                    help="with --serve: every prompt has this length (default: uniform in [128, 2048])")
+    ap.add_argument("--serve-new", type=int, default=256, metavar="TOKENS", help="with --serve: new tokens per request")
     ap.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64")
     ap.add_argument("--no-prefill", action="store_true", help="skip the 2,048-token prefill (for profiling decode)")
     ap.add_argument("--prefill-only", action="store_true",
@@ -307,17 +310,19 @@ def main() -> int:
     page = 16
     if args.serve:
         n = args.serve
+        longest = (args.serve_prompt or 2048) + args.serve_new
         engine = Engine(config=cfg, seed=0, dtype="bfloat16", device=dev, kv_page_size=page,
-                        kv_num_pages=n * (2304 // page + 2), kv_max_batch=n, kv_max_seq=2304 + 64, max_batch_size=n,
+                        kv_num_pages=n * (longest // page + 2), kv_max_batch=n, kv_max_seq=longest + 64, max_batch_size=n,
                         max_batch_tokens=8192, chunked_prefill_tokens=512)
-        serve_workload(engine, cfg, min(n, 8), 16)                     # warm-up: kernels, graphs, allocator
-        dt, pt, gt, steps_run, pre = serve_workload(engine, cfg, n, 256)
+        serve_workload(engine, cfg, min(n, 8), 16, prompt_len=min(args.serve_prompt, 1024))   # warm-up: kernels, graphs
+        dt, pt, gt, steps_run, pre = serve_workload(engine, cfg, n, args.serve_new, prompt_len=args.serve_prompt)
         print(json.dumps({"metric": "served tokens/s (prompt + generated), chunked prefill mixed with decode",
                           "value": round((pt + gt) / dt, 1), "generated_tok_s": round(gt / dt, 1), "unit": "tokens/s",
                           "seconds": round(dt, 3), "steps": steps_run, "requests": n, "prompt_tokens": pt,
                           "generated_tokens": gt, "preemptions": pre, "dtype": "bf16", "n_gpus": 1,
-                          "config": {"model": f"Qwen2.5-{args.shape.upper()} shape", "prefill_chunk": 512,
-                                     "new_tokens": 256, "kv_page": page}, "impl": "ours"}))
+                          "config": {"model": f"Qwen2.5-{args.shape.upper()} shape", "layers": cfg.num_hidden_layers,
+                                     "prompts": args.serve_prompt or "uniform in [128, 2048]", "prefill_chunk": 512,
+                                     "new_tokens": args.serve_new, "kv_page": page}, "impl": "ours"}))
         return 0
     if args.prefill_only:
         engine = Engine(config=cfg, seed=0, dtype="bfloat16", device=dev, kv_page_size=page,
