@@ -26,13 +26,13 @@ SHAPES = {
 LENS = [70, 37]
 
 
-def make(shape, dtype, cuda_kernels):
+def make(shape, dtype, cuda_kernels, max_pos=512, num_pages=16):
     from inferflux_b200.config import Qwen2Config
     from inferflux_b200.engine import ModelRunner
     from inferflux_b200.models import random_model
-    cfg = Qwen2Config(num_hidden_layers=1, max_position_embeddings=512, **SHAPES[shape])
+    cfg = Qwen2Config(num_hidden_layers=1, max_position_embeddings=max_pos, **SHAPES[shape])
     model = random_model(cfg, seed=5, dtype=dtype, device="cuda:0", norm_jitter=0.2)
-    return cfg, model, ModelRunner(model, cuda_kernels, page_size=16, num_pages=16, max_seqs=4)
+    return cfg, model, ModelRunner(model, cuda_kernels, page_size=16, num_pages=num_pages, max_seqs=4)
 
 
 def oracle(cfg, model, reqs, weights_as):
@@ -76,3 +76,43 @@ def test_real_layer_shapes_in_bfloat16(shape, cuda_kernels):
         agree = np.mean([np.mean(got[r].argmax(-1) == want[r].argmax(-1)) for r in want])
         assert agree > 0.9, f"{shape}: the best token agrees at only {agree:.2f} of the positions"
     cuda_kernels.check_errors()
+
+
+def test_long_context_at_a_real_shape(cuda_kernels):
+    """2,500 tokens through one layer of the 1.5B shape in bfloat16: whole, in portions of 512 and
+    300 behind the growing prefix, and with the last tokens decoded one by one (clusters of blocks
+    over thousands of keys); logits at a few dozen positions against the plain implementation."""
+    from inferflux_b200.engine import StepEntry
+    cfg, model, runner = make("1.5b", "bfloat16", cuda_kernels, max_pos=4096, num_pages=2 * 160)
+    T = 2500
+    toks = helpers.random_tokens(cfg.vocab_size, T, 901)
+    wanted = sorted(set(list(range(0, T, 97)) + [127, 128, 255, 256, 511, 512, 1023, 1024, 2047, 2048] + list(range(T - 12, T))))
+    from inferflux_b200.weights import random_tensors
+    from plain import plain_qwen2
+    W = random_tensors(model.expected_tensors(), 5, dtype=torch.bfloat16, device="cuda:0", norm_jitter=0.2)
+    W.pop("lm_head.weight", None)
+    full = plain_qwen2.forward(cfg.to_dict(), W, toks, dtype=torch.float64)
+    want = full[torch.tensor(wanted, device=full.device)].cpu().numpy()
+    del full, W
+    torch.cuda.empty_cache()
+    scale = float(np.abs(want).max())
+
+    def run(cuts, name):
+        got, pos = {}, 0
+        for n in cuts:
+            here = [p - pos for p in wanted if pos <= p < pos + n]
+            out = runner.step([StepEntry(name, toks[pos:pos + n], here)])
+            for k, p in enumerate(here):
+                got[pos + p] = out[k].float().cpu().numpy()
+            pos += n
+        runner.end_request(name)
+        assert pos == T
+        return np.stack([got[p] for p in wanted])
+
+    cuttings = {"whole": [T], "portions": [512, 300] * 3 + [T - 3 * 812], "tail": [T - 12] + [1] * 12}
+    for name, cuts in cuttings.items():
+        got = run(cuts, name)
+        d = np.abs(got - want).max(axis=1)
+        assert float(d.max()) < 0.03 * scale, f"{name}: position {wanted[int(d.argmax())]} differs by {float(d.max())} (scale {scale})"
+    cuda_kernels.check_errors()
+    assert not runner.cache.live_requests()
