@@ -99,11 +99,12 @@ class CudaKernels:
         for fn in ("ifx_embed", "ifx_rmsnorm", "ifx_silu_mul", "ifx_residual_add", "ifx_gather_rows",
                    "ifx_scatter_i32", "ifx_rope_append", "ifx_attention_generic", "ifx_gemm_generic",
                    "ifx_gemm_cublas_bf16", "ifx_cublas_init", "ifx_argmax", "ifx_penalties", "ifx_logit_bias",
-                   "ifx_sample", "ifx_attention_mma_supports", "ifx_attention_prefill_bf16",
+                   "ifx_sample", "ifx_sample_blocks", "ifx_attention_mma_supports", "ifx_attention_prefill_bf16",
                    "ifx_attention_prefill_tcgen05", "ifx_attention_prefill_tcgen05_supports", "ifx_attention_decode_max_splits",
                    "ifx_attention_decode_bf16", "ifx_gemm_skinny", "ifx_residual_add_partial",
                    "ifx_reduce_partial", "ifx_reduce_add_rmsnorm", "ifx_argmax_chunks", "ifx_relay_i32", "ifx_prenorm", "ifx_scale_rows"):
             getattr(self.lib, fn).restype = ctypes.c_int
+        self.lib.ifx_sample_scratch_bytes.restype = ctypes.c_longlong
         with torch.cuda.device(self.device):
             _check(self.lib.ifx_cublas_init(), "cublas init")
         if os.environ.get("INFERFLUX_B200_PDL", "1") == "0":      # for measurements: no overlap of consecutive kernels
@@ -115,6 +116,7 @@ class CudaKernels:
         # scratch of the many-block reduce + norm: sums of squares per (row, chunk), a ticket per row
         self._norm_sumsq = torch.zeros(128 * 64, dtype=torch.float32, device=self.device)
         self._norm_tickets = torch.zeros(128, dtype=torch.int32, device=self.device)
+        self._sample_scratch, self._sample_capacity = None, 0   # zeroed once; the sampling kernels leave it zero
         self._argmax_val = torch.zeros(256 * 32, dtype=torch.float32, device=self.device)
         self._argmax_idx = torch.zeros(256 * 32, dtype=torch.int32, device=self.device)
         self._argmax_tickets = torch.zeros(256, dtype=torch.int32, device=self.device)
@@ -459,7 +461,24 @@ class CudaKernels:
                                        _stream()), "logit_bias")
         self.launches += 1
 
-    def sample(self, logits, temperature, top_k, top_p, min_p, seed_lo, seed_hi, step):
+    def sample(self, logits, temperature, top_k, top_p, min_p, seed_lo, seed_hi, step, features=3):
+        """One draw per row (see sampling.cu).  Rows are spread over many blocks; `features` says which
+        filters any row uses (bit 0: top-k, bit 1: top-p) so that the passes of the others are not launched."""
+        R, V = logits.shape
+        out = torch.empty((R,), dtype=torch.int32, device=logits.device)
+        if R > self._sample_capacity:                    # the scratch's layout goes with its capacity
+            self._sample_capacity = max(64, 1 << (R - 1).bit_length())
+            self._sample_scratch = torch.zeros(int(self.lib.ifx_sample_scratch_bytes(self._sample_capacity)),
+                                               dtype=torch.uint8, device=logits.device)
+        passes = 3 + (1 if features & 3 else 0) + (2 if features & 1 else 0) + (3 if features & 2 else 0)
+        _check(self.lib.ifx_sample_blocks(_ptr(logits), _ptr(temperature), _ptr(top_k), _ptr(top_p), _ptr(min_p),
+                                          _ptr(seed_lo), _ptr(seed_hi), _ptr(step), _ptr(out), R, V, int(features),
+                                          _ptr(self._sample_scratch), self._sample_capacity, _stream()), "sample")
+        self.launches += passes
+        return out
+
+    def sample_one_block(self, logits, temperature, top_k, top_p, min_p, seed_lo, seed_hi, step):
+        """The same draw with one block per row and thresholds by bisection (kept for comparison)."""
         R, V = logits.shape
         probs = torch.empty((R, V), dtype=torch.float32, device=logits.device)
         out = torch.empty((R,), dtype=torch.int32, device=logits.device)

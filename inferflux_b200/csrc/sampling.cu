@@ -1,4 +1,4 @@
-// Sampling from float32 logits [rows, vocab], one block per row.
+// Sampling from float32 logits [rows, vocab].
 //
 // What the reference samples with (runtime/backends/cuda/native/gpu_sampler.cu):
 // argmax with ties to the lowest index (:124-156), softmax(logits / temperature)
@@ -10,9 +10,12 @@
 // request's seed, counter = the request's step), so a row's draw does not depend
 // on what else is in the batch.  top-k and min-p thresholds are taken as well.
 //
-// Thresholds are found by bisection on the bit pattern of the probability (for
-// non-negative floats the bit pattern orders like the value), which gives the
-// exact k-th largest value, or the exact nucleus boundary, in 31 passes without a sort.
+// Thresholds are found on the bit pattern of the probability (for non-negative floats
+// the bit pattern orders like the value) without a sort.  sample_kernel has one block per
+// row and bisects (31 passes: the exact k-th largest value, the exact nucleus boundary); the
+// sampler the engine uses spreads a row over many blocks and descends by radix (see
+// "sampling over many blocks" below): 33 us instead of 142 for a plain temperature draw from
+// 152,064 logits, 100 us instead of 1,400 with top-k, min-p and top-p together.
 #include "common.cuh"
 
 namespace ifx {
@@ -270,6 +273,385 @@ sample_kernel(const float* __restrict__ logits, float* __restrict__ probs, const
   if (threadIdx.x == 0) out[r] = result >= 0 ? result : (last_kept >= 0 ? last_kept : top.i);
 }
 
+
+// ------------------------------------------------------- sampling over many blocks
+// The same draw as sample_kernel, but a row is spread over `chunks` blocks and the
+// thresholds are found by a radix descent (three levels of 10 bits of the element's
+// bit pattern, a histogram of counts and masses per level) instead of 31 passes of
+// bisection.  An element is e = exp(logit / T - max), so the largest is exactly 1.  Masses
+// are sums of e in fixed point (2^-40), i.e. integers: their sums do not depend on the
+// order of the additions, so blocks may add them with atomics and the draw stays
+// reproducible.  Passes are separate launches; the block that finishes a row last (a
+// ticket per row) does the row's small sequential step and leaves tickets and histograms
+// zero for the next use.
+constexpr int kBins = 1024;
+constexpr int kSmpThreads = 256;
+constexpr int kSmpMaxChunks = 32;
+
+struct SampleRowState {
+  float inv_t;                    // 1 / temperature
+  float rowmax;                   // max of logit / T
+  int argidx;                     // where it is (lowest index)
+  int flags;                      // bit 0: draws (temperature > 0), 1: top-k, 2: top-p
+  unsigned thr_key;               // elements with bits >= thr_key are kept
+  unsigned prefix;                // radix descent: the bits fixed so far
+  unsigned k_res;                 // top-k descent: how many more elements from the current range
+  int pick_chunk;                 // the chunk the draw falls into
+  unsigned long long need;        // top-p descent: how much more mass from the current range
+  unsigned long long target;      // the draw, as mass inside pick_chunk
+  float top_p;
+  int pad;
+};
+
+__device__ __forceinline__ float smp_elem(const float* __restrict__ row, int i, float inv_t, float rowmax) {
+  return expf(row[i] * inv_t - rowmax);
+}
+__device__ __forceinline__ unsigned long long smp_mass(float e) { return __float2ull_rz(e * 1099511627776.0f); }
+
+__device__ __forceinline__ unsigned long long block_sum_u64(unsigned long long v, unsigned long long* scratch /* 32 */) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  unsigned long long r = lane < nwarps ? scratch[lane] : 0ull;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) r += __shfl_xor_sync(0xffffffffu, r, o);
+  return r;
+}
+
+// Takes the row's ticket; true in every thread of the block that came last.  The caller's writes
+// before the call are visible to that block after it.
+__device__ __forceinline__ bool smp_last_block(int* tickets, int row, int chunks, int* flag_smem) {
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int t = atomicAdd(&tickets[row], 1);
+    *flag_smem = t == chunks - 1;
+    if (*flag_smem) tickets[row] = 0;
+  }
+  __syncthreads();
+  const bool last = *flag_smem != 0;
+  if (last) __threadfence();
+  return last;
+}
+
+// From the top bin down: the largest bin b whose suffix (bins >= b) reaches `want`, and the
+// suffix above it.  Counts (by_mass = false) or masses.  One block, 256 threads, 4 bins each.
+__device__ void smp_scan_bins(const unsigned* __restrict__ cnt, const unsigned long long* __restrict__ mass,
+                              bool by_mass, unsigned long long want, int* bin_out, unsigned long long* above_out,
+                              unsigned long long* scan_smem /* 256 + 32 */, int* found_smem) {
+  const int t = threadIdx.x;                          // thread t owns bins 1023 - 4t ... 1020 - 4t, top first
+  unsigned long long v[4], mine = 0ull;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int b = kBins - 1 - (4 * t + j);
+    v[j] = by_mass ? __ldcg(&mass[b]) : (unsigned long long)__ldcg(&cnt[b]);
+    mine += v[j];
+  }
+  // inclusive scan over the threads (Hillis-Steele in shared memory; integers: any order gives the same)
+  scan_smem[t] = mine;
+  if (t == 0) *found_smem = 0x7fffffff;
+  __syncthreads();
+  for (int off = 1; off < kSmpThreads; off <<= 1) {
+    const unsigned long long add = t >= off ? scan_smem[t - off] : 0ull;
+    __syncthreads();
+    scan_smem[t] += add;
+    __syncthreads();
+  }
+  const unsigned long long incl = scan_smem[t], excl = incl - mine;
+  if (excl < want && incl >= want) atomicMin(found_smem, t);
+  __syncthreads();
+  if (t == *found_smem) {
+    unsigned long long run = excl;
+    int b = kBins - 1 - 4 * t;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      if (run + v[j] >= want) {
+        b = kBins - 1 - (4 * t + j);
+        break;
+      }
+      run += v[j];
+    }
+    *bin_out = b;
+    *above_out = run;
+  }
+  if (*found_smem == 0x7fffffff && t == 0) {          // `want` beyond everything there is: the lowest bin
+    *bin_out = 0;
+    *above_out = 0ull;
+  }
+  __syncthreads();
+}
+
+struct SampleScratch {
+  SampleRowState* state;
+  int* tickets;
+  float* part_val;
+  int* part_idx;
+  unsigned long long* chunk_mass;
+  unsigned* cnt_a;
+  unsigned long long* mass_a;
+  unsigned* cnt_b;
+  unsigned long long* mass_b;
+};
+
+__global__ void __launch_bounds__(kSmpThreads)
+smp_max_kernel(const float* __restrict__ logits, const float* __restrict__ temperature,
+               const int* __restrict__ top_k, const float* __restrict__ top_p, const float* __restrict__ min_p,
+               int* __restrict__ out, int vocab, int chunks, int features, SampleScratch sc) {
+  __shared__ ArgBest scratch[32];
+  __shared__ int last_flag;
+  const int r = blockIdx.x, c = blockIdx.y;
+  const int per = (vocab + chunks - 1) / chunks;
+  const int begin = min(vocab, c * per), end = min(vocab, begin + per);
+  const float temp = temperature[r];
+  const bool draws = temp > 0.0f;
+  const float inv_t = draws ? 1.0f / temp : 1.0f;
+  ArgBest b = block_argmax(logits + (size_t)r * vocab + begin, end - begin, inv_t, scratch);
+  if (threadIdx.x == 0) {
+    sc.part_val[r * chunks + c] = end > begin ? b.v : -INFINITY;
+    sc.part_idx[r * chunks + c] = begin + b.i;
+  }
+  if (!smp_last_block(sc.tickets, r, chunks, &last_flag) || threadIdx.x >= 32) return;
+  ArgBest best{-INFINITY, 0x7fffffff};
+  for (int k = threadIdx.x; k < chunks; k += 32) {
+    ArgBest o{__ldcg(&sc.part_val[r * chunks + k]), __ldcg(&sc.part_idx[r * chunks + k])};
+    best = better(best, o);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    ArgBest other{__shfl_xor_sync(0xffffffffu, best.v, o), __shfl_xor_sync(0xffffffffu, best.i, o)};
+    best = better(best, other);
+  }
+  if (threadIdx.x == 0) {
+    if (best.i == 0x7fffffff) best = ArgBest{0.0f, 0};
+    SampleRowState st = {};
+    st.inv_t = inv_t;
+    st.rowmax = best.v;
+    st.argidx = best.i;
+    const int k = top_k[r];
+    const float tp = top_p[r], mp = min_p[r];
+    // a filter whose passes the caller did not ask for (features) is off for the row as well
+    st.flags = (draws ? 1 : 0) | ((draws && (features & 1) && k > 0 && k < vocab) ? 2 : 0) |
+               ((draws && (features & 2) && tp > 0.0f && tp < 1.0f) ? 4 : 0);
+    st.thr_key = (draws && mp > 0.0f) ? __float_as_uint(fminf(mp, 1.0f)) : 0u;   // e >= min_p * (largest e = 1)
+    st.k_res = (st.flags & 2) ? (unsigned)k : 0u;
+    st.top_p = tp;
+    sc.state[r] = st;
+    if (!draws) out[r] = best.i;
+  }
+}
+
+// LEVEL 1, 2, 3: bits [29:20], [19:10], [9:0] of the element.  PURPOSE 0: top-k (counts), 1: top-p (masses).
+// Level 1 serves both and lands in histogram A; the others in B.
+template <int LEVEL, int PURPOSE>
+__global__ void __launch_bounds__(kSmpThreads)
+smp_hist_kernel(const float* __restrict__ logits, int vocab, int chunks, SampleScratch sc) {
+  __shared__ unsigned cnt_s[kBins];
+  __shared__ unsigned long long mass_s[kBins];
+  __shared__ unsigned long long scan_s[kSmpThreads + 32];
+  __shared__ int last_flag, found_s, bin_s;
+  __shared__ unsigned long long above_s;
+  const int r = blockIdx.x, c = blockIdx.y;
+  const SampleRowState st = sc.state[r];
+  const int want_flag = LEVEL == 1 ? 6 : (PURPOSE == 0 ? 2 : 4);
+  if (!(st.flags & 1) || !(st.flags & want_flag)) return;
+  constexpr int SHIFT = LEVEL == 1 ? 20 : (LEVEL == 2 ? 10 : 0);
+  for (int i = threadIdx.x; i < kBins; i += blockDim.x) {
+    cnt_s[i] = 0u;
+    mass_s[i] = 0ull;
+  }
+  __syncthreads();
+  const int per = (vocab + chunks - 1) / chunks;
+  const int begin = min(vocab, c * per), end = min(vocab, begin + per);
+  const float* row = logits + (size_t)r * vocab;
+  for (int i = begin + threadIdx.x; i < end; i += blockDim.x) {
+    const float e = smp_elem(row, i, st.inv_t, st.rowmax);
+    const unsigned bits = __float_as_uint(e);
+    if (LEVEL == 1 || (bits >> (SHIFT + 10)) == st.prefix) {
+      const int bin = (bits >> SHIFT) & (kBins - 1);
+      atomicAdd(&cnt_s[bin], 1u);
+      atomicAdd(&mass_s[bin], smp_mass(e));
+    }
+  }
+  __syncthreads();
+  unsigned* cnt_g = (LEVEL == 1 ? sc.cnt_a : sc.cnt_b) + (size_t)r * kBins;
+  unsigned long long* mass_g = (LEVEL == 1 ? sc.mass_a : sc.mass_b) + (size_t)r * kBins;
+  for (int i = threadIdx.x; i < kBins; i += blockDim.x) {
+    if (cnt_s[i]) {
+      atomicAdd(&cnt_g[i], cnt_s[i]);
+      atomicAdd(&mass_g[i], mass_s[i]);
+    }
+  }
+  if (!smp_last_block(sc.tickets, r, chunks, &last_flag)) return;
+  // ---- the row's step: where does the target fall among the bins
+  const bool scan_k = LEVEL == 1 ? (st.flags & 2) != 0 : PURPOSE == 0;
+  const bool scan_p = LEVEL != 1 && PURPOSE == 1;
+  if (scan_k || scan_p) {
+    smp_scan_bins(cnt_g, mass_g, scan_p, scan_p ? st.need : (unsigned long long)st.k_res, &bin_s, &above_s, scan_s,
+                  &found_s);
+    if (threadIdx.x == 0) {
+      SampleRowState* g = sc.state + r;
+      const unsigned prefix = LEVEL == 1 ? (unsigned)bin_s : ((st.prefix << 10) | (unsigned)bin_s);
+      g->prefix = prefix;
+      if (scan_p) g->need = st.need - above_s; else g->k_res = st.k_res - (unsigned)above_s;
+      if (LEVEL == 3) g->thr_key = max(st.thr_key, prefix);        // the descent has all 30 bits
+    }
+  }
+  // Histogram B is used once per level; A stays for the top-p descent unless the row has none.
+  if (LEVEL != 1 || !(st.flags & 4)) {
+    __syncthreads();
+    for (int i = threadIdx.x; i < kBins; i += blockDim.x) {
+      cnt_g[i] = 0u;
+      mass_g[i] = 0ull;
+    }
+  }
+}
+
+// Kept mass per chunk.  PASS 0: before the nucleus (rows with top-p start its descent from histogram A
+// here; the others get their draw); PASS 1: rows with top-p, after it.
+template <int PASS>
+__global__ void __launch_bounds__(kSmpThreads)
+smp_mass_kernel(const float* __restrict__ logits, const unsigned* __restrict__ seed_lo,
+                const unsigned* __restrict__ seed_hi, const unsigned* __restrict__ step, int vocab, int chunks,
+                SampleScratch sc) {
+  __shared__ unsigned long long scan_s[kSmpThreads + 32];
+  __shared__ int last_flag, found_s, bin_s;
+  __shared__ unsigned long long above_s;
+  const int r = blockIdx.x, c = blockIdx.y;
+  const SampleRowState st = sc.state[r];
+  if (!(st.flags & 1) || (PASS == 1 && !(st.flags & 4))) return;
+  const int per = (vocab + chunks - 1) / chunks;
+  const int begin = min(vocab, c * per), end = min(vocab, begin + per);
+  const float* row = logits + (size_t)r * vocab;
+  unsigned long long mine = 0ull;
+  for (int i = begin + threadIdx.x; i < end; i += blockDim.x) {
+    const float e = smp_elem(row, i, st.inv_t, st.rowmax);
+    if (__float_as_uint(e) >= st.thr_key) mine += smp_mass(e);
+  }
+  const unsigned long long total = block_sum_u64(mine, scan_s);
+  if (threadIdx.x == 0) sc.chunk_mass[r * chunks + c] = total;
+  if (!smp_last_block(sc.tickets, r, chunks, &last_flag)) return;
+  unsigned long long kept = 0ull;
+  for (int k = 0; k < chunks; ++k) kept += __ldcg(&sc.chunk_mass[r * chunks + k]);
+  if (PASS == 0 && (st.flags & 4)) {
+    // nucleus: the smallest set of the largest kept elements whose mass reaches top_p of the kept mass
+    unsigned long long need = (unsigned long long)((double)st.top_p * (double)kept);
+    if (need < 1ull) need = 1ull;
+    if (need > kept) need = kept;
+    unsigned* cnt_g = sc.cnt_a + (size_t)r * kBins;
+    unsigned long long* mass_g = sc.mass_a + (size_t)r * kBins;
+    smp_scan_bins(cnt_g, mass_g, true, need, &bin_s, &above_s, scan_s, &found_s);
+    if (threadIdx.x == 0) {
+      sc.state[r].prefix = (unsigned)bin_s;
+      sc.state[r].need = need - above_s;
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < kBins; i += blockDim.x) {
+      cnt_g[i] = 0u;
+      mass_g[i] = 0ull;
+    }
+    return;
+  }
+  if (threadIdx.x == 0) {
+    const uint32_t bits = philox_uniform_bits(seed_lo[r], seed_hi[r], step[r], 0u, 0u, 0u);
+    const double u = (double)(bits >> 8) * (1.0 / 16777216.0);
+    unsigned long long target = (unsigned long long)(u * (double)kept);
+    if (kept > 0ull && target >= kept) target = kept - 1ull;
+    int pick = -1;
+    unsigned long long run = 0ull;
+    for (int k = 0; k < chunks; ++k) {
+      const unsigned long long m = __ldcg(&sc.chunk_mass[r * chunks + k]);
+      if (m > 0ull && target < run + m) {
+        pick = k;
+        break;
+      }
+      run += m;
+    }
+    sc.state[r].pick_chunk = pick;
+    sc.state[r].target = target - run;
+  }
+}
+
+// The draw: in the chosen chunk, the first kept element (in index order) whose running mass exceeds the target.
+__global__ void __launch_bounds__(kSmpThreads)
+smp_pick_kernel(const float* __restrict__ logits, int* __restrict__ out, int vocab, int chunks, SampleScratch sc) {
+  __shared__ unsigned long long scan_s[kSmpThreads];
+  __shared__ int chosen;
+  const int r = blockIdx.x, c = blockIdx.y;
+  const SampleRowState st = sc.state[r];
+  if (!(st.flags & 1)) return;
+  if (st.pick_chunk < 0) {                               // nothing kept (cannot happen: the largest element always is)
+    if (c == 0 && threadIdx.x == 0) out[r] = st.argidx;
+    return;
+  }
+  if (c != st.pick_chunk) return;
+  const int per = (vocab + chunks - 1) / chunks;
+  const int begin = min(vocab, c * per), end = min(vocab, begin + per);
+  const int seg = (end - begin + kSmpThreads - 1) / kSmpThreads;
+  const int lo = min(end, begin + (int)threadIdx.x * seg), hi = min(end, lo + seg);
+  const float* row = logits + (size_t)r * vocab;
+  unsigned long long mine = 0ull;
+  for (int i = lo; i < hi; ++i) {
+    const float e = smp_elem(row, i, st.inv_t, st.rowmax);
+    if (__float_as_uint(e) >= st.thr_key) mine += smp_mass(e);
+  }
+  scan_s[threadIdx.x] = mine;
+  if (threadIdx.x == 0) chosen = 0x7fffffff;
+  __syncthreads();
+  for (int off = 1; off < kSmpThreads; off <<= 1) {
+    const unsigned long long add = (int)threadIdx.x >= off ? scan_s[threadIdx.x - off] : 0ull;
+    __syncthreads();
+    scan_s[threadIdx.x] += add;
+    __syncthreads();
+  }
+  const unsigned long long incl = scan_s[threadIdx.x], excl = incl - mine;
+  if (mine > 0ull && excl <= st.target && st.target < incl) atomicMin(&chosen, (int)threadIdx.x);
+  __syncthreads();
+  if (chosen == 0x7fffffff) {
+    if (threadIdx.x == 0) out[r] = st.argidx;
+    return;
+  }
+  if ((int)threadIdx.x != chosen) return;
+  unsigned long long run = excl;
+  int pick = st.argidx;
+  for (int i = lo; i < hi; ++i) {
+    const float e = smp_elem(row, i, st.inv_t, st.rowmax);
+    if (__float_as_uint(e) >= st.thr_key) {
+      run += smp_mass(e);
+      if (run > st.target) {
+        pick = i;
+        break;
+      }
+    }
+  }
+  out[r] = pick;
+}
+
+static size_t smp_align(size_t v) { return (v + 255) & ~(size_t)255; }
+
+static size_t smp_layout(SampleScratch* sc, unsigned char* base, int rows) {
+  size_t off = 0;
+  auto take = [&](size_t bytes) {
+    unsigned char* p = base ? base + off : nullptr;
+    off += smp_align(bytes);
+    return p;
+  };
+  SampleScratch s;
+  s.state = reinterpret_cast<SampleRowState*>(take((size_t)rows * sizeof(SampleRowState)));
+  s.tickets = reinterpret_cast<int*>(take((size_t)rows * 4));
+  s.part_val = reinterpret_cast<float*>(take((size_t)rows * kSmpMaxChunks * 4));
+  s.part_idx = reinterpret_cast<int*>(take((size_t)rows * kSmpMaxChunks * 4));
+  s.chunk_mass = reinterpret_cast<unsigned long long*>(take((size_t)rows * kSmpMaxChunks * 8));
+  s.cnt_a = reinterpret_cast<unsigned*>(take((size_t)rows * kBins * 4));
+  s.mass_a = reinterpret_cast<unsigned long long*>(take((size_t)rows * kBins * 8));
+  s.cnt_b = reinterpret_cast<unsigned*>(take((size_t)rows * kBins * 4));
+  s.mass_b = reinterpret_cast<unsigned long long*>(take((size_t)rows * kBins * 8));
+  if (sc) *sc = s;
+  return off;
+}
+
 }  // namespace ifx
 
 using namespace ifx;
@@ -319,6 +701,45 @@ int ifx_sample(const float* logits, float* probs, const float* temperature, cons
   if (vocab <= 0) return IFX_E_BADARG;
   sample_kernel<<<rows, kSampleThreads, 0, stream>>>(logits, probs, temperature, top_k, top_p, min_p, seed_lo, seed_hi,
                                                      step, out, vocab);
+  IFX_CHECK_LAUNCH();
+  return 0;
+}
+
+// Bytes of scratch ifx_sample_blocks needs for up to `capacity` rows.  The scratch must be zero before
+// its first use; the kernels leave it ready for the next call with the same capacity (the places of its
+// parts depend on the capacity, not on a call's rows).
+long long ifx_sample_scratch_bytes(int capacity) {
+  return (long long)smp_layout(nullptr, nullptr, capacity < 1 ? 1 : capacity);
+}
+
+// The draw of ifx_sample with every row spread over many blocks.  features: bit 0 = some row has top-k,
+// bit 1 = some row has top-p (the passes those need are launched only then; a row without them skips them).
+int ifx_sample_blocks(const float* logits, const float* temperature, const int* top_k, const float* top_p,
+                      const float* min_p, const unsigned* seed_lo, const unsigned* seed_hi, const unsigned* step,
+                      int* out, int rows, int vocab, int features, void* scratch, int capacity,
+                      cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (vocab <= 0 || rows > 65535 || scratch == nullptr) return IFX_E_BADARG;
+  if (rows > capacity) return IFX_E_TOOBIG;
+  SampleScratch sc;
+  smp_layout(&sc, static_cast<unsigned char*>(scratch), capacity);
+  int chunks = vocab / 2048;
+  chunks = chunks < 1 ? 1 : (chunks > kSmpMaxChunks ? kSmpMaxChunks : chunks);
+  const dim3 grid(rows, chunks);
+  smp_max_kernel<<<grid, kSmpThreads, 0, stream>>>(logits, temperature, top_k, top_p, min_p, out, vocab, chunks, features,
+                                                    sc);
+  if (features & 3) smp_hist_kernel<1, 0><<<grid, kSmpThreads, 0, stream>>>(logits, vocab, chunks, sc);
+  if (features & 1) {
+    smp_hist_kernel<2, 0><<<grid, kSmpThreads, 0, stream>>>(logits, vocab, chunks, sc);
+    smp_hist_kernel<3, 0><<<grid, kSmpThreads, 0, stream>>>(logits, vocab, chunks, sc);
+  }
+  smp_mass_kernel<0><<<grid, kSmpThreads, 0, stream>>>(logits, seed_lo, seed_hi, step, vocab, chunks, sc);
+  if (features & 2) {
+    smp_hist_kernel<2, 1><<<grid, kSmpThreads, 0, stream>>>(logits, vocab, chunks, sc);
+    smp_hist_kernel<3, 1><<<grid, kSmpThreads, 0, stream>>>(logits, vocab, chunks, sc);
+    smp_mass_kernel<1><<<grid, kSmpThreads, 0, stream>>>(logits, seed_lo, seed_hi, step, vocab, chunks, sc);
+  }
+  smp_pick_kernel<<<grid, kSmpThreads, 0, stream>>>(logits, out, vocab, chunks, sc);
   IFX_CHECK_LAUNCH();
   return 0;
 }

@@ -72,4 +72,6 @@ class Sampler:
             self._dev([r.params.min_p for r in rows], torch.float32),
             self._dev([as_i32(r.seed & 0xFFFFFFFF) for r in rows], torch.int32),
             self._dev([as_i32((r.seed >> 32) & 0xFFFFFFFF) for r in rows], torch.int32),
-            self._dev([as_i32(r.step & 0xFFFFFFFF) for r in rows], torch.int32))
+            self._dev([as_i32(r.step & 0xFFFFFFFF) for r in rows], torch.int32),
+            features=(1 if any(r.params.top_k > 0 for r in rows) else 0) |
+                     (2 if any(0.0 < r.params.top_p < 1.0 for r in rows) else 0))

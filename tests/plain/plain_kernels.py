@@ -139,7 +139,7 @@ class PlainKernels:
         for r, t, b in zip(rows.tolist(), tokens.tolist(), bias.tolist()):
             logits[r, t] += b
 
-    def sample(self, logits, temperature, top_k, top_p, min_p, seed_lo, seed_hi, step):
+    def sample(self, logits, temperature, top_k, top_p, min_p, seed_lo, seed_hi, step, features=3):
         R, V = logits.shape
         out = torch.empty((R,), dtype=torch.int32, device=logits.device)
         for r in range(R):

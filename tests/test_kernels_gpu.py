@@ -429,6 +429,51 @@ def test_sampling_matches_plain(cuda_kernels):
     assert agree >= 6 * rows - 2, f"only {agree} of {6 * rows} draws agree with the plain sampler"
 
 
+@pytest.mark.parametrize("vocab", [700, 9001, 152064])
+def test_sampling_over_many_blocks_against_one_block(cuda_kernels, vocab):
+    """The many-block sampler (radix descent on counts and fixed-point masses) draws what the
+    one-block sampler (bisection on float sums) draws, up to elements that sit on a threshold;
+    whatever it draws lies in the kept set; twice in a row (its scratch must be left zero)."""
+    from plain.plain_kernels import kept_mask
+    rows = 24
+    logits = rnd(rows, vocab, seed=51, scale=2.5)
+    logits[3, 17] = logits[3, 400]                       # ties at a threshold
+    g = torch.Generator().manual_seed(5)
+    temperature = (torch.rand(rows, generator=g) * 1.5 + 0.3)
+    temperature[5] = 0.0
+    top_k = torch.tensor([0, 1, 5, 50, 0, 0, 0, 1000, 3, 0, 0, 20] * 2, dtype=torch.int32)
+    top_p = torch.tensor([1.0, 1.0, 1.0, 0.9, 0.5, 0.3, 0.95, 0.8, 1.0, 0.05, 0.999, 0.7] * 2)
+    min_p = torch.tensor([0, 0, 0, 0, 0, 0, 0.05, 0, 0.3, 0, 0, 0.01] * 2, dtype=torch.float32)
+    seed_lo = torch.arange(rows, dtype=torch.int32) + 77
+    z = torch.zeros(rows, dtype=torch.int32)
+    dev = lambda t: t.to(DEV)
+    agree = total = 0
+    for step in range(8):
+        st = torch.full((rows,), step, dtype=torch.int32)
+        args = [dev(temperature), dev(top_k), dev(top_p), dev(min_p), dev(seed_lo), dev(z), dev(st)]
+        got = cuda_kernels.sample(logits, *args).tolist()
+        again = cuda_kernels.sample(logits, *args).tolist()
+        assert got == again, "the same call drew differently the second time"
+        few = cuda_kernels.sample(logits[:5].contiguous(), *[a[:5].contiguous() for a in args]).tolist()
+        assert few == got[:5], "a row drew differently in a smaller batch"
+        one = cuda_kernels.sample_one_block(logits, *args).tolist()
+        agree += sum(int(a == b) for a, b in zip(got, one))
+        total += rows
+        assert got[5] == int(torch.argmax(logits[5]))
+        for r in range(rows):
+            if float(temperature[r]) > 0:
+                p = torch.softmax(logits[r].cpu() / float(temperature[r]), -1)
+                keep = kept_mask(p, int(top_k[r]), float(top_p[r]), float(min_p[r]))
+                assert bool(keep[got[r]]) or float(p[got[r]]) >= 0.999 * float(p[keep].min()), (r, got[r])
+    assert agree >= total - 4, f"only {agree} of {total} draws agree with the one-block sampler"
+    # filters the caller says nobody uses are not applied: the plain temperature draw
+    plain = cuda_kernels.sample(logits, dev(temperature), dev(top_k), dev(top_p), dev(min_p * 0), dev(seed_lo), dev(z), dev(z),
+                                features=0).tolist()
+    want = cuda_kernels.sample_one_block(logits, dev(temperature), dev(top_k * 0), dev(top_p * 0 + 1), dev(min_p * 0),
+                                         dev(seed_lo), dev(z), dev(z)).tolist()
+    assert sum(int(a == b) for a, b in zip(plain, want)) >= rows - 1
+
+
 def test_sampling_distribution_and_batch_independence(cuda_kernels):
     vocab = 50
     logits = torch.log(torch.arange(1, vocab + 1, dtype=torch.float32)).repeat(4096, 1).to(DEV)
