@@ -67,9 +67,43 @@ def check_tensors(found: Dict[str, Tuple[int, ...]], expected: Dict[str, TensorS
         raise WeightError(missing, unexpected, wrong, where)
 
 
+class _Staging:
+    """Two pinned buffers through which mapped file bytes go to the device: the host copy of one
+    chunk runs while the other chunk's transfer is in flight."""
+
+    CHUNK = 64 << 20
+
+    def __init__(self, device):
+        self.device = torch.device(device)
+        self.bufs = [torch.empty(self.CHUNK, dtype=torch.uint8).pin_memory() for _ in range(2)]
+        self.events = [torch.cuda.Event() for _ in range(2)]
+        self.turn = 0
+
+    def to_device(self, t: torch.Tensor) -> torch.Tensor:
+        src = t.reshape(-1).view(torch.uint8)
+        out = torch.empty(t.shape, dtype=t.dtype, device=self.device)
+        dst = out.reshape(-1).view(torch.uint8)
+        for off in range(0, src.numel(), self.CHUNK):
+            n = min(self.CHUNK, src.numel() - off)
+            i = self.turn
+            self.turn ^= 1
+            self.events[i].synchronize()                  # the buffer's last transfer is done
+            self.bufs[i][:n].copy_(src[off:off + n])
+            dst[off:off + n].copy_(self.bufs[i][:n], non_blocking=True)
+            self.events[i].record()
+        return out
+
+    def finish(self):
+        for e in self.events:
+            e.synchronize()
+
+
 def load_weights(model_dir, expected: Dict[str, TensorSpec], device="cpu") -> Dict[str, torch.Tensor]:
-    """All tensors of a model folder that `expected` names, on `device`."""
+    """All tensors of a model folder that `expected` names, on `device`.  To a CUDA device the bytes go
+    from the mapped file through pinned buffers; the dtype is converted there."""
     shards = open_model_shards(model_dir)
+    dev = torch.device(device)
+    staging = _Staging(dev) if dev.type == "cuda" else None
     try:
         owner = {}
         for sh in shards:
@@ -80,8 +114,15 @@ def load_weights(model_dir, expected: Dict[str, TensorSpec], device="cpu") -> Di
         for n, spec in expected.items():
             if n not in owner or spec.ignored:
                 continue
-            t = owner[n].tensor(n)
-            out[n] = t.to(stored_dtype(t.dtype)).to(device)
+            if staging is None:
+                t = owner[n].tensor(n)
+                out[n] = t.to(stored_dtype(t.dtype))
+            else:
+                t = owner[n].view(n)
+                out[n] = staging.to_device(t).to(stored_dtype(t.dtype))
+                del t
+        if staging is not None:
+            staging.finish()
         return out
     finally:
         for sh in shards:

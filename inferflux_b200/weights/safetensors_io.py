@@ -36,7 +36,7 @@ def _itemsize(dt: torch.dtype) -> int:
 
 
 class SafetensorsFile:
-    """One memory-mapped .safetensors file; tensors are copied out on request."""
+    """One memory-mapped .safetensors file; `tensor` copies a tensor out, `view` maps it."""
 
     def __init__(self, path):
         self.path = Path(path)
@@ -46,7 +46,8 @@ class SafetensorsFile:
         if size < 8:
             raise SafetensorsError(f"{self.path}: {size} bytes is too short for a safetensors header")
         self._fh = open(self.path, "rb")
-        self._mm = mmap.mmap(self._fh.fileno(), 0, access=mmap.ACCESS_READ)
+        # a private (copy-on-write) mapping: nothing is written, but a writable buffer is what torch maps
+        self._mm = mmap.mmap(self._fh.fileno(), 0, access=mmap.ACCESS_COPY)
         (n,) = struct.unpack("<Q", self._mm[:8])
         if n > _MAX_HEADER or 8 + n > size:
             raise SafetensorsError(f"{self.path}: header length {n} does not fit the file ({size} bytes)")
@@ -100,9 +101,21 @@ class SafetensorsFile:
         buf = bytearray(self._mm[self._data_start + begin:self._data_start + end])
         return torch.frombuffer(buf, dtype=dt).reshape(shape)
 
+    def view(self, name: str) -> torch.Tensor:
+        """A CPU tensor over the mapping itself: no copy, valid until `close`.  Falls back to a copy
+        where the tensor's bytes do not start on a multiple of its element size."""
+        dt, shape, begin, end = self._info[name]
+        start = self._data_start + begin
+        if end == begin or start % _itemsize(dt):
+            return self.tensor(name)
+        numel = (end - begin) // _itemsize(dt)
+        return torch.frombuffer(self._mm, dtype=dt, count=numel, offset=start).reshape(shape)
+
     def close(self) -> None:
         try:
             self._mm.close()
+        except BufferError:
+            pass                       # a view still points into the mapping: it goes when the view does
         finally:
             self._fh.close()
 
