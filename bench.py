@@ -337,9 +337,10 @@ def main() -> int:
                           "impl": "ours"}))
         return 0
     biggest = max(args.batch, 1 if args.no_points else 64)
-    pages = biggest * (CONTEXT // page + 2)
+    longest = CONTEXT + 4 * (warmup + steps) + 8 + biggest       # a prompt plus the most new tokens time_decode allows
+    pages = biggest * (longest // page + 2)
     engine = Engine(config=cfg, seed=0, dtype="bfloat16", device=dev, kv_page_size=page, kv_num_pages=pages,
-                    kv_max_batch=biggest, kv_max_seq=CONTEXT + 64, max_batch_size=biggest,
+                    kv_max_batch=biggest, kv_max_seq=longest, max_batch_size=biggest,
                     max_batch_tokens=8192, chunked_prefill_tokens=2048)
 
     clock = ClockSampler()
@@ -375,8 +376,9 @@ def main() -> int:
         "e2e": {"value": round(args.batch * 1000.0 / e2e_ms, 1), "unit": "tokens/s",
                 "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h), "ms_per_step": round(e2e_ms, 4)},
         "gpu_launches": int(round(launches * steps)),
-        "prefill": {"value": round(PREFILL_TOKENS * 1000.0 / prefill_ms, 1), "tokens": PREFILL_TOKENS,
-                    "ms": round(prefill_ms, 3), "frac": round(pf_frac, 4)},
+        "prefill": None if args.no_prefill else
+        {"value": round(PREFILL_TOKENS * 1000.0 / prefill_ms, 1), "tokens": PREFILL_TOKENS,
+         "ms": round(prefill_ms, 3), "frac": round(pf_frac, 4)},
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
                      "frac": round(achieved / pk["hbm_gbs"], 4)},
         "points": points,
