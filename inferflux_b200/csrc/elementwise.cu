@@ -98,7 +98,7 @@ __global__ void rmsnorm_kernel(float* __restrict__ x, const void* __restrict__ d
 // Loads are issued in batches before anything depends on them: with a handful of
 // rows the kernel's time is a few round trips to L2, not bandwidth.
 constexpr int kNormChunk = 512;
-constexpr int kNormBatch = 8;
+constexpr int kNormBatch = 12;
 
 template <typename T>
 __global__ void __launch_bounds__(128)
