@@ -32,11 +32,27 @@ __global__ void rope_append_kernel(const T* __restrict__ qkv, const float* __res
   const size_t src_off = (size_t)t * width + (size_t)head * d;
   const T* src = qkv ? qkv + src_off : nullptr;
   const float* psrc = qkv_partial ? qkv_partial + src_off : nullptr;
-  auto load = [&](int e) -> float {
-    if (psrc == nullptr) return to_f32(src[e]);
-    float v = 0.0f;
-    for (int s = 0; s < num_splits; ++s) v += psrc[(size_t)s * split_stride + e];
-    return v;
+  auto load2 = [&](int e0, int e1, float& a, float& c) {     // the two elements of a pair, K slices added in order
+    if (psrc == nullptr) {
+      a = to_f32(src[e0]);
+      c = to_f32(src[e1]);
+      return;
+    }
+    a = c = 0.0f;
+    for (int s0 = 0; s0 < num_splits; s0 += 8) {                // 16 loads in flight a round
+      float va[8], vc[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const bool in = s0 + j < num_splits;
+        va[j] = in ? __ldcg(psrc + (size_t)(s0 + j) * split_stride + e0) : 0.0f;
+        vc[j] = in ? __ldcg(psrc + (size_t)(s0 + j) * split_stride + e1) : 0.0f;
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        a += va[j];
+        c += vc[j];
+      }
+    }
   };
   const float* b = bias ? bias + (size_t)head * d : nullptr;
   const int pos = positions[t];
@@ -84,7 +100,10 @@ __global__ void rope_append_kernel(const T* __restrict__ qkv, const float* __res
   if (dst == nullptr) return;
   for (int j = threadIdx.x; j < d / 2; j += blockDim.x) {
     const Pair p = j == (int)threadIdx.x ? first : prepare(j);
-    float a = load(p.e0) + p.b0, c = load(p.e1) + p.b1;
+    float a, c;
+    load2(p.e0, p.e1, a, c);
+    a += p.b0;
+    c += p.b1;
     if (p.turn) {
       const float ra = a * p.cs - c * p.sn;
       const float rc = a * p.sn + c * p.cs;
