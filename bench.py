@@ -165,7 +165,11 @@ def time_decode(engine, cfg, batch, steps, warmup, sampler_clock=None):
     import torch
     from inferflux_b200.engine import StepEntry
     total = warmup + steps
-    prompt_len = CONTEXT - 2 * total - 2
+    # The last timed step ends at CONTEXT: the prompt leaves room for both timed loops and for the tokens
+    # the first requests decode while the last prompts are still prefilled (8,192 prompt tokens a step).
+    # So no step of the timed loops is the first of a longer context class (its CUDA graph would be
+    # captured inside the timing).
+    prompt_len = CONTEXT - 2 * total - 2 - (-(-batch * CONTEXT // 8192) + 2)
     prompts = random_prompts(cfg, batch, prompt_len, seed=batch)
     bring_to_decode(engine, prompts, max_tokens=4 * total + 8 + batch)   # the first ones decode while the last prefill
     runner, kernels = engine.runner, engine.kernels

@@ -191,7 +191,14 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
       const int m = threadIdx.x - 64;             // the 128 epilogue threads, one token each
       if (m < M) {
         float total = 0.0f;
-        for (int c = 0; c < sumsq_chunks; ++c) total += __ldcg(&row_sumsq[(size_t)m * sumsq_chunks + c]);
+        for (int c0 = 0; c0 < sumsq_chunks; c0 += 8) {              // 8 loads in flight, added in chunk order
+          float part[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            part[j] = c0 + j < sumsq_chunks ? __ldcg(&row_sumsq[(size_t)m * sumsq_chunks + c0 + j]) : 0.0f;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) total += part[j];
+        }
         row_scale[m] = rsqrtf(total / (float)K + eps);
       }
       asm volatile("bar.sync 1, 128;" ::: "memory");
