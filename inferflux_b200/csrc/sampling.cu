@@ -34,9 +34,19 @@ __device__ __forceinline__ ArgBest better(ArgBest a, ArgBest b) {
 
 __device__ ArgBest block_argmax(const float* __restrict__ row, int n, float mul, ArgBest* scratch /* 32 */) {
   ArgBest best{-INFINITY, 0x7fffffff};
-  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+  const int bd = blockDim.x;
+  int i = threadIdx.x;
+  for (; i + 7 * bd < n; i += 8 * bd) {              // eight loads in flight, compared in index order
+    float v[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] = row[i + j * bd] * mul;
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      if (v[j] > best.v) best = ArgBest{v[j], i + j * bd};   // strict: the lowest index of a thread's stride wins
+  }
+  for (; i < n; i += bd) {
     const float v = row[i] * mul;
-    if (v > best.v) best = ArgBest{v, i};            // strict: the lowest index of a thread's stride wins
+    if (v > best.v) best = ArgBest{v, i};
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
