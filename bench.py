@@ -60,6 +60,24 @@ class ClockSampler:
         self._thread = None
 
     def _run(self):
+        try:                                    # NVML in this process: a sample every 20 ms (reading only)
+            import pynvml
+            pynvml.nvmlInit()
+            h = pynvml.nvmlDeviceGetHandleByIndex(0)
+            try:
+                get_reasons = pynvml.nvmlDeviceGetCurrentClocksEventReasons
+            except AttributeError:
+                get_reasons = pynvml.nvmlDeviceGetCurrentClocksThrottleReasons
+            mx = pynvml.nvmlDeviceGetMaxClockInfo(h, pynvml.NVML_CLOCK_SM)
+            while not self._stop.is_set():
+                bits = int(get_reasons(h))
+                self.rows.append([str(pynvml.nvmlDeviceGetClockInfo(h, pynvml.NVML_CLOCK_SM)), str(mx), "",
+                                  "Active" if bits & 0x8 else "Not Active", "Active" if bits & 0x40 else "Not Active",
+                                  "Active" if bits & 0x20 else "Not Active", "Active" if bits & 0x4 else "Not Active"])
+                self._stop.wait(0.02)
+            return
+        except Exception:
+            pass
         while not self._stop.is_set():
             try:
                 out = subprocess.run(["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}",
