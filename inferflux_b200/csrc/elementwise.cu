@@ -14,6 +14,8 @@ int g_pdl_enabled = 1;
 template <typename T>
 __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ tokens,
                              float* __restrict__ out, int hidden, int vocab) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int t = blockIdx.x;
   const int id = tokens[t];
   float* o = out + (size_t)t * hidden;
@@ -35,6 +37,8 @@ __global__ void rmsnorm_kernel(float* __restrict__ x, const void* __restrict__ d
                                const float* __restrict__ w, T* __restrict__ out, int hidden, float eps,
                                int num_splits, size_t split_stride) {
   __shared__ float scratch[32];
+  pdl_launch_dependents();
+  pdl_wait();
   const size_t row = blockIdx.x;
   float* xr = x + row * hidden;
   const T* dr = ADD == 1 ? reinterpret_cast<const T*>(delta_raw) + row * hidden : nullptr;
@@ -328,10 +332,18 @@ __global__ void residual_add_kernel(float* __restrict__ x, const T* __restrict__
 // x += sum over splits of float32 partial sums [splits, rows*hidden], in split order.
 __global__ void residual_add_partial_kernel(float* __restrict__ x, const float* __restrict__ part, size_t total,
                                             int num_splits) {
+  pdl_launch_dependents();
+  pdl_wait();
   size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= total) return;
   float d = 0.0f;
-  for (int s = 0; s < num_splits; ++s) d += part[(size_t)s * total + idx];
+  for (int s0 = 0; s0 < num_splits; s0 += 8) {             // eight loads in flight, added in split order
+    float v[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] = s0 + j < num_splits ? __ldcg(&part[(size_t)(s0 + j) * total + idx]) : 0.0f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) d += v[j];
+  }
   x[idx] += d;
 }
 
@@ -349,6 +361,8 @@ __global__ void reduce_partial_kernel(const float* __restrict__ part, const floa
 
 __global__ void gather_rows_kernel(const float* __restrict__ x, const int* __restrict__ rows,
                                    float* __restrict__ out, int hidden, int num_src_rows) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int r = blockIdx.x;
   int src = rows[r];
   float* o = out + (size_t)r * hidden;
@@ -396,14 +410,12 @@ int ifx_embed(const void* table, const int* tokens, float* out, int num_tokens, 
   if (hidden <= 0 || vocab <= 0) return IFX_E_BADARG;
   const int threads = hidden >= 1024 ? 256 : 128;
   if (dtype == IFX_DT_F32)
-    embed_kernel<float><<<num_tokens, threads, 0, stream>>>((const float*)table, tokens, out, hidden, vocab);
+    return launch_pdl(embed_kernel<float>, dim3(num_tokens), dim3(threads), 0, stream, 1, (const float*)table, tokens, out,
+                      hidden, vocab);
   else if (dtype == IFX_DT_BF16)
-    embed_kernel<__nv_bfloat16><<<num_tokens, threads, 0, stream>>>((const __nv_bfloat16*)table, tokens, out,
-                                                                    hidden, vocab);
-  else
-    return IFX_E_DTYPE;
-  IFX_CHECK_LAUNCH();
-  return 0;
+    return launch_pdl(embed_kernel<__nv_bfloat16>, dim3(num_tokens), dim3(threads), 0, stream, 1,
+                      (const __nv_bfloat16*)table, tokens, out, hidden, vocab);
+  return IFX_E_DTYPE;
 }
 
 // delta == nullptr: plain norm of x.  Otherwise x += delta, then the norm of the sum;
@@ -414,8 +426,9 @@ int ifx_rmsnorm(float* x, const void* delta, const float* w, void* out, int rows
   if (hidden <= 0 || num_splits < 0) return IFX_E_BADARG;
   const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
   const size_t stride = (size_t)rows * hidden;
-#define IFX_NORM(T, ADD) \
-  rmsnorm_kernel<T, ADD><<<rows, threads, 0, stream>>>(x, delta, w, (T*)out, hidden, eps, num_splits, stride)
+#define IFX_NORM(T, ADD)                                                                                        \
+  return launch_pdl(rmsnorm_kernel<T, ADD>, dim3(rows), dim3(threads), 0, stream, 1, x, delta, w, (T*)out, hidden, eps, \
+                    num_splits, stride)
   if (dtype == IFX_DT_F32) {
     if (!delta) IFX_NORM(float, 0);
     else if (num_splits > 0) IFX_NORM(float, 2);
@@ -424,12 +437,9 @@ int ifx_rmsnorm(float* x, const void* delta, const float* w, void* out, int rows
     if (!delta) IFX_NORM(__nv_bfloat16, 0);
     else if (num_splits > 0) IFX_NORM(__nv_bfloat16, 2);
     else IFX_NORM(__nv_bfloat16, 1);
-  } else {
-    return IFX_E_DTYPE;
   }
 #undef IFX_NORM
-  IFX_CHECK_LAUNCH();
-  return 0;
+  return IFX_E_DTYPE;
 }
 
 // The same as ifx_rmsnorm with partial sums, over many blocks.  sumsq: float32
@@ -496,9 +506,8 @@ int ifx_scale_rows(const void* pre, const float* sumsq, void* out, int rows, int
 int ifx_residual_add_partial(float* x, const float* part, int rows, int hidden, int num_splits, cudaStream_t stream) {
   if (rows <= 0 || num_splits <= 0) return 0;
   const size_t total = (size_t)rows * hidden;
-  residual_add_partial_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(x, part, total, num_splits);
-  IFX_CHECK_LAUNCH();
-  return 0;
+  return launch_pdl(residual_add_partial_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, 1, x, part,
+                    total, num_splits);
 }
 
 int ifx_reduce_partial(const float* part, const float* bias, void* out, int rows, int cols, int num_splits, int dtype,
@@ -555,9 +564,7 @@ int ifx_residual_add(float* x, const void* delta, int rows, int hidden, int dtyp
 int ifx_gather_rows(const float* x, const int* rows, float* out, int num_rows, int hidden, int num_src_rows,
                     cudaStream_t stream) {
   if (num_rows <= 0) return 0;
-  gather_rows_kernel<<<num_rows, 256, 0, stream>>>(x, rows, out, hidden, num_src_rows);
-  IFX_CHECK_LAUNCH();
-  return 0;
+  return launch_pdl(gather_rows_kernel, dim3(num_rows), dim3(256), 0, stream, 1, x, rows, out, hidden, num_src_rows);
 }
 
 int ifx_relay_i32(int* dst, const int* dst_index, const int* src, const int* src_index, int n, int dst_size,

@@ -82,6 +82,8 @@ __global__ void argmax_chunks_kernel(const float* __restrict__ logits, int* __re
                                      int* __restrict__ tickets) {
   __shared__ ArgBest scratch[32];
   __shared__ int is_last;
+  pdl_launch_dependents();
+  pdl_wait();
   const int row = blockIdx.x, chunk = blockIdx.y;
   const int per = (vocab + chunks - 1) / chunks;
   const int begin = min(vocab, chunk * per), end = min(vocab, begin + per);
@@ -682,10 +684,8 @@ int ifx_argmax_chunks(const float* logits, int* out, int rows, int vocab, int ch
                       int* tickets, cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (vocab <= 0 || chunks <= 0 || chunks > 1024) return IFX_E_BADARG;
-  dim3 grid(rows, chunks);
-  argmax_chunks_kernel<<<grid, 256, 0, stream>>>(logits, out, vocab, chunks, part_val, part_idx, tickets);
-  IFX_CHECK_LAUNCH();
-  return 0;
+  return launch_pdl(argmax_chunks_kernel, dim3(rows, chunks), dim3(256), 0, stream, 1, logits, out, vocab, chunks,
+                    part_val, part_idx, tickets);
 }
 
 int ifx_penalties(float* logits, const int* tokens, const int* counts, const float* rep, const float* freq,
