@@ -1,9 +1,9 @@
 // Weight-streaming matrix product for few tokens on the 5th-generation tensor
-// cores: out[M, N] = act[M, K] . W[N, K]^T for M <= 128 (decode batches and short
-// prompt portions), where the time is the time to read W once.
+// cores: out[M, N] = act[M, K] . W[N, K]^T for M <= 256 (decode batches, short prompts
+// and small prompt portions), where the time is the time to read W once.
 //
 // The operands are swapped: the weight tile is the MMA's A operand (128 weight rows
-// = the 128 TMEM lanes) and the M token rows, padded to 16/32/64/128, are its N.
+// = the 128 TMEM lanes) and the M token rows, padded to 16/32/64/128/256, are its N.
 // One thread block owns a tile of 128 weight rows and one slice of K:
 //
 //   warp 0     producer: TMA (cp.async.bulk.tensor, 128-byte swizzle) of the weight
@@ -186,10 +186,9 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     pdl_wait();                                   // nothing is written before the kernel in front has finished
     // Rows that arrive pre-normed (x * w without the norm's row scale) get the scale here:
     // rsqrt(mean(x^2) + eps) from the per-chunk sums of squares the norm kernel left.
-    __shared__ float row_scale[128];
+    __shared__ float row_scale[NPAD < 128 ? 128 : NPAD];
     if (row_sumsq != nullptr) {
-      const int m = threadIdx.x - 64;             // the 128 epilogue threads, one token each
-      if (m < M) {
+      for (int m = threadIdx.x - 64; m < M; m += 128) {   // the 128 epilogue threads share the tokens
         float total = 0.0f;
         for (int c0 = 0; c0 < sumsq_chunks; c0 += 8) {              // 8 loads in flight, added in chunk order
           float part[8];
@@ -291,8 +290,9 @@ static int launch_skinny(const CUtensorMap& mw, const CUtensorMap& ma, const flo
                          int sumsq_chunks, float eps, int* error_flag, cudaStream_t stream) {
   const int total_kblocks = (K + kTileK - 1) / kTileK;
   const int per_split = (total_kblocks + splits - 1) / splits;
-  // as many stages as fit ~100 KB (two blocks per SM), at most the k-blocks of a split; SWIGLU blocks own their SM
-  const size_t budget = MODE == MODE_SWIGLU ? 200 * 1024 : 100 * 1024;
+  // as many stages as fit ~100 KB (two blocks per SM), at most the k-blocks of a split; SWIGLU blocks and blocks
+  // with 256 token rows (32 KB of activations a stage) own their SM
+  const size_t budget = (MODE == MODE_SWIGLU || NPAD == 256) ? 200 * 1024 : 100 * 1024;
   int stages = 8;
   while (stages > 2 && skinny_smem_bytes(NPAD, MODE, stages) > budget) --stages;
   if (stages > per_split) stages = per_split < 2 ? 2 : per_split;
@@ -313,7 +313,7 @@ static int launch_skinny(const CUtensorMap& mw, const CUtensorMap& ma, const flo
 
 using namespace ifx;
 
-// act [M, K] and W [rows, K] bfloat16, M <= 128, K % 8 == 0, both 16-byte aligned.
+// act [M, K] and W [rows, K] bfloat16, M <= 256, K % 8 == 0, both 16-byte aligned.
 // mode 0: out[M, N] (+ bias) bfloat16 or float32, splits must be 1.
 // mode 1: partials[splits, M, N] float32.
 // mode 2: W holds N gate rows at 0 and N up rows at up_row_offset; out[M, N] = silu(gate) * up, bfloat16.
@@ -325,7 +325,7 @@ extern "C" int ifx_gemm_skinny(const void* act, const void* W, const float* bias
                                const float* row_sumsq, int sumsq_chunks, float eps, int* error_flag,
                                cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
-  if (K <= 0 || M > 128 || splits <= 0 || splits > 65535 || error_flag == nullptr) return IFX_E_BADARG;
+  if (K <= 0 || M > 256 || splits <= 0 || splits > 65535 || error_flag == nullptr) return IFX_E_BADARG;
   if (mode == MODE_STORE && splits != 1) return IFX_E_BADARG;
   if (mode == MODE_SWIGLU && (splits != 1 || out_is_f32)) return IFX_E_BADARG;
   if (mode == MODE_PARTIAL && partials == nullptr) return IFX_E_BADARG;
@@ -334,7 +334,7 @@ extern "C" int ifx_gemm_skinny(const void* act, const void* W, const float* bias
   CUtensorMap mw, ma;
   int rc = weight_map(&mw, W, w_rows, K);
   if (rc) return rc;
-  const int npad = M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128));
+  const int npad = M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : (M <= 128 ? 128 : 256)));
   rc = make_tensor_map_bf16(&ma, act, M, K, npad);
   if (rc) return rc;
 #define LAUNCH(NP, MD) \
@@ -345,7 +345,8 @@ extern "C" int ifx_gemm_skinny(const void* act, const void* W, const float* bias
     case 16: LAUNCH(16, MD);        \
     case 32: LAUNCH(32, MD);        \
     case 64: LAUNCH(64, MD);        \
-    default: LAUNCH(128, MD);       \
+    case 128: LAUNCH(128, MD);      \
+    default: LAUNCH(256, MD);       \
   }
   if (mode == MODE_STORE) { BY_NPAD(MODE_STORE) }
   if (mode == MODE_PARTIAL) { BY_NPAD(MODE_PARTIAL) }

@@ -94,10 +94,12 @@ def test_gemm_bfloat16(cuda_kernels, M, N, K, out_dtype):
 
 
 @pytest.mark.parametrize("M,N,K", [(1, 128, 64), (8, 256, 512), (17, 1000, 200), (33, 300, 328), (64, 3584, 1024),
-                                   (100, 130, 72), (128, 520, 4104), (5, 4608, 3584)])
-def test_gemm_tcgen05_few_rows(cuda_kernels, M, N, K):
+                                   (100, 130, 72), (128, 520, 4104), (5, 4608, 3584), (129, 264, 520), (200, 1000, 328),
+                                   (256, 384, 4104)])
+def test_gemm_tcgen05_few_rows(cuda_kernels, monkeypatch, M, N, K):
     """The weight-streaming tensor-core product: plain store (bfloat16 and float32 out, with
     bias), K split into partial sums and their consumers, and the fused silu(gate) * up."""
+    monkeypatch.setattr(type(cuda_kernels), "SKINNY_MAX_ROWS", 256)    # the kernel's own limit, not the routing's
     from inferflux_b200.csrc import PartialSum
     a = rnd(M, K, dtype=torch.bfloat16, seed=20, scale=0.5)
     w = rnd(N, K, dtype=torch.bfloat16, seed=21, scale=0.1)
@@ -134,10 +136,11 @@ def test_gemm_tcgen05_few_rows(cuda_kernels, M, N, K):
     cuda_kernels.check_errors()
 
 
-@pytest.mark.parametrize("T,H,N", [(1, 64, 128), (8, 3584, 512), (33, 1000, 264), (128, 520, 130)])
-def test_prenormed_rows_through_the_product(cuda_kernels, T, H, N):
+@pytest.mark.parametrize("T,H,N", [(1, 64, 128), (8, 3584, 512), (33, 1000, 264), (128, 520, 130), (250, 520, 264)])
+def test_prenormed_rows_through_the_product(cuda_kernels, monkeypatch, T, H, N):
     """The norm that leaves its row scale to the product: prenorm + linear equals
     add_rmsnorm + linear, for every epilogue of the few-rows product."""
+    monkeypatch.setattr(type(cuda_kernels), "SKINNY_MAX_ROWS", 256)    # the kernel's own limit, not the routing's
     from inferflux_b200.csrc import PartialSum, ScaledRows
     x = rnd(T, H, seed=30)
     parts = PartialSum(rnd(3, T, H, seed=31, scale=0.3), torch.bfloat16)
