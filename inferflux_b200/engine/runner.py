@@ -11,6 +11,8 @@ anything is launched (the reference does the same for slots and positions,
 """
 from __future__ import annotations
 
+import os
+
 from typing import Hashable, List, Optional, Sequence
 
 import torch
@@ -28,6 +30,13 @@ class ModelRunner:
     """A loaded model, its cache and the kernel table: everything `step` needs."""
 
     MAX_GRAPHS = 24
+    # A step that is one request's prompt portion of at least this many tokens (chunked prefill brings
+    # the same portion size again and again) can be captured too, at its second occurrence; few of these
+    # graphs are kept, because each holds the step's activations.  Off unless INFERFLUX_B200_PORTION_GRAPHS=1:
+    # measured at the 7B shape a graph saves 0.3 ms on a portion of 129 tokens and nothing on 2,048 (the
+    # host is ahead of the device anyway), while its capture stalls one step for 20 ms or more.
+    PORTION_GRAPH_MIN_TOKENS = 64
+    MAX_PORTION_GRAPHS = 4
 
     def __init__(self, model, kernels, page_size: int = 16, num_pages: int = 256, max_seqs: int = 8,
                  max_seq_len: Optional[int] = None, cache_dtype: Optional[torch.dtype] = None,
@@ -50,6 +59,8 @@ class ModelRunner:
         self.cuda_graphs = bool(cuda_graphs) and self.device.type == "cuda" and all(
             p.graph_safe for _n, p in model.named_parts())
         self._graphs = {}              # key -> [uses, graph or None, static buffer, static logits]
+        self._portion_graphs = {}      # the same for prompt portions
+        self.portion_graphs = os.environ.get("INFERFLUX_B200_PORTION_GRAPHS", "0") == "1"
         self.graph_replays = 0
 
     # ---------------------------------------------------------------- requests
@@ -141,18 +152,21 @@ class ModelRunner:
             self.kernels.relay_i32(ctx.token_ids, ctx.relay_dst, ctx.relay_ids, ctx.relay_src)
 
     def _forward(self, ctx: StepContext, entries) -> torch.Tensor:
-        if not self.cuda_graphs or ctx.max_span != 1 or ctx.num_logit_rows != ctx.num_tokens:
+        decode_only = ctx.max_span == 1 and ctx.num_logit_rows == ctx.num_tokens
+        one_portion = self.portion_graphs and len(entries) == 1 and ctx.num_tokens >= self.PORTION_GRAPH_MIN_TOKENS
+        if not self.cuda_graphs or not (decode_only or one_portion):
             self._relay(ctx)
             return self.model.forward(ctx, self.cache)
         bucket = 256
         while bucket < ctx.max_kv_len:
             bucket *= 2
         key = (ctx.num_tokens, bucket, ctx.layout_key())
-        slot = self._graphs.get(key)
+        graphs, most = (self._graphs, self.MAX_GRAPHS) if decode_only else (self._portion_graphs, self.MAX_PORTION_GRAPHS)
+        slot = graphs.get(key)
         if slot is None:                                   # first time: run as is (also warms every kernel up)
-            if len(self._graphs) >= self.MAX_GRAPHS:
-                self._graphs.pop(next(iter(self._graphs)))
-            self._graphs[key] = [1, None, None, None]
+            if len(graphs) >= most:
+                graphs.pop(next(iter(graphs)))
+            graphs[key] = [1, None, None, None]
             self._relay(ctx)
             return self.model.forward(ctx, self.cache)
         slot[0] += 1

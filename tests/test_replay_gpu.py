@@ -166,3 +166,31 @@ def test_decode_steps_replayed_from_a_cuda_graph(dtype, model_dirs, tiny_configs
     got = helpers.collect(steps, helpers.run_steps_in_process(runner, steps), cfg.vocab_size)
     assert runner.graph_replays >= 30
     check(got, {k: oracle[name][dtype][k] for k in reqs}, dtype, f"graph replay {dtype}")
+
+
+@pytest.mark.parametrize("name,dtype", [("E", "bfloat16"), ("E", "float32"), ("C", "bfloat16")])
+def test_prompt_portions_replayed_from_a_cuda_graph(name, dtype, model_dirs, tiny_configs, cuda_kernels):
+    """Chunked prefill brings the same portion size again and again: from its second occurrence a
+    one-request portion runs from a captured graph (behind a growing prefix, through the window,
+    with and without wanted logits); the logits are those of the plain implementation."""
+    from inferflux_b200.engine import ModelRunner, StepEntry
+    from inferflux_b200.models import load_model
+    cfg, page = tiny_configs[name]
+    d, _ = model_dirs[name]
+    toks = helpers.random_tokens(cfg.vocab_size, 370, 811)
+    want = helpers.plain_logits(d, {"r": toks}, weights_as=torch.bfloat16 if dtype == "bfloat16" else None)["r"]
+    _c, model = load_model(d, dtype=dtype, device="cuda:0")
+    runner = ModelRunner(model, cuda_kernels, page_size=page, num_pages=64, max_seqs=2, cuda_graphs=True)
+    runner.portion_graphs = True                             # an option (INFERFLUX_B200_PORTION_GRAPHS=1), off by default
+    got, pos = {}, 0
+    for k, n in enumerate([64] * 5 + [50]):
+        here = list(range(n)) if k != 2 else []              # one portion asks for nothing
+        out = runner.step([StepEntry("r", toks[pos:pos + n], here)])
+        for j, p in enumerate(here):
+            got[pos + p] = out[j].float().cpu().numpy()
+        pos += n
+    runner.end_request("r")
+    assert runner.graph_replays >= 2, "no portion ran from a graph"
+    rows = sorted(got)
+    check({"r": np.stack([got[p] for p in rows])}, {"r": want[rows]}, dtype, f"portion graphs {name}/{dtype}")
+    cuda_kernels.check_errors()
