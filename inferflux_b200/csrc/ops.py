@@ -67,15 +67,16 @@ def _ptr(t: Optional[torch.Tensor]):
     return ctypes.c_void_p(0 if t is None else t.data_ptr())
 
 
-# The current stream's handle, asked for at every launch: torch's own accessor when it is there (a
-# plain integer, a fraction of a microsecond), else through the Stream object (several microseconds).
+# The current stream's handle of the current device, asked for at every launch: torch's own accessors
+# when they are there (plain integers, a fraction of a microsecond), else through the Stream object
+# (several microseconds).
 _RAW_STREAM = getattr(torch._C, "_cuda_getCurrentRawStream", None)
-_DEVICE_INDEX = 0            # set by CudaKernels: the engine runs on one device
+_RAW_DEVICE = getattr(torch._C, "_cuda_getDevice", None)
 
 
 def _stream():
-    if _RAW_STREAM is not None:
-        return ctypes.c_void_p(_RAW_STREAM(_DEVICE_INDEX))
+    if _RAW_STREAM is not None and _RAW_DEVICE is not None:
+        return ctypes.c_void_p(_RAW_STREAM(_RAW_DEVICE()))
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
@@ -103,8 +104,6 @@ class CudaKernels:
         if not torch.cuda.is_available():
             raise BuildError("no CUDA device: the engine has no CPU path")
         self.device = torch.device(device)
-        global _DEVICE_INDEX
-        _DEVICE_INDEX = self.device.index if self.device.index is not None else torch.cuda.current_device()
         self.lib = load_library()
         for fn in ("ifx_embed", "ifx_rmsnorm", "ifx_silu_mul", "ifx_residual_add", "ifx_gather_rows",
                    "ifx_scatter_i32", "ifx_rope_append", "ifx_attention_generic", "ifx_gemm_generic",
