@@ -194,3 +194,47 @@ def test_prompt_portions_replayed_from_a_cuda_graph(name, dtype, model_dirs, tin
     rows = sorted(got)
     check({"r": np.stack([got[p] for p in rows])}, {"r": want[rows]}, dtype, f"portion graphs {name}/{dtype}")
     cuda_kernels.check_errors()
+
+
+def test_twenty_thousand_tokens_against_the_plain_implementation(tmp_path, cuda_kernels):
+    """Positions beyond 16 bits, a block table of 1,250 entries, a window of 9,000 keys on the second
+    layer, head size 64 (the tensor-core prompt attention, clusters of blocks in decode): a request of
+    20,000 tokens whole and in portions with decoded tokens at the end, against the plain
+    implementation run on the GPU in float64."""
+    from inferflux_b200.config import Qwen2Config
+    from inferflux_b200.engine import ModelRunner, StepEntry
+    from inferflux_b200.models import load_model
+    from plain import plain_qwen2
+    cfg = Qwen2Config(hidden_size=136, num_hidden_layers=2, num_attention_heads=6, num_key_value_heads=2, head_dim=64,
+                      intermediate_size=264, vocab_size=640, max_position_embeddings=40000, rope_theta=300000.0,
+                      rms_norm_eps=2e-6, tie_word_embeddings=False, use_sliding_window=True, sliding_window=9000,
+                      max_window_layers=1)
+    T = 20000
+    d = helpers.write_tiny_model(cfg, tmp_path / "long", seed=3)
+    toks = helpers.random_tokens(cfg.vocab_size, T, 77)
+    wanted = sorted(set(list(range(0, T, 997)) + [T - 1 - i for i in range(6)] +
+                        [8191, 8192, 8999, 9000, 9001, 16383, 16384]))
+    raw, W = plain_qwen2.load_model_dir(d)
+    W = {k: v.to(torch.bfloat16).cuda() for k, v in W.items()}
+    full = plain_qwen2.forward(raw, W, toks, dtype=torch.float64)
+    want = full[torch.tensor(wanted, device=full.device)].cpu().numpy()
+    del full, W
+    torch.cuda.empty_cache()
+    scale = float(np.abs(want).max())
+    _c, model = load_model(d, dtype="bfloat16", device="cuda:0")
+    runner = ModelRunner(model, cuda_kernels, page_size=16, num_pages=T // 16 + 8, max_seqs=2, cuda_graphs=True)
+    for name, cuts in (("whole", [T]), ("portions", [4096, 3000, 5000, 1, T - 12097 - 6] + [1] * 6)):
+        got, pos = {}, 0
+        for n in cuts:
+            here = [p - pos for p in wanted if pos <= p < pos + n]
+            out = runner.step([StepEntry(name, toks[pos:pos + n], here)])
+            for j, p in enumerate(here):
+                got[pos + p] = out[j].float().cpu().numpy()
+            pos += n
+        runner.end_request(name)
+        assert pos == T
+        diff = np.abs(np.stack([got[p] for p in wanted]) - want).max(axis=1)
+        assert float(diff.max()) < 0.03 * scale, \
+            f"{name}: position {wanted[int(diff.argmax())]} differs by {float(diff.max())} (scale {scale})"
+    cuda_kernels.check_errors()
+    assert not runner.cache.live_requests()
