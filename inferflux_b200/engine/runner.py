@@ -60,6 +60,9 @@ class ModelRunner:
             p.graph_safe for _n, p in model.named_parts())
         self._graphs = {}              # key -> [uses, graph or None, static buffer, static logits]
         self._portion_graphs = {}      # the same for prompt portions
+        # All graphs allocate from one pool: they never run at the same time, so the activations of one
+        # reuse the memory of the others (a graph of its own pool each would hold them all at once).
+        self._graph_pool = torch.cuda.graph_pool_handle() if self.cuda_graphs else None
         self.portion_graphs = os.environ.get("INFERFLUX_B200_PORTION_GRAPHS", "0") == "1"
         self.graph_replays = 0
 
@@ -179,7 +182,7 @@ class ModelRunner:
             torch.cuda.synchronize(self.device)
             graph = torch.cuda.CUDAGraph()
             launches = self.kernels.launches
-            with torch.cuda.graph(graph):
+            with torch.cuda.graph(graph, pool=self._graph_pool):
                 static_logits = self.model.forward(ctx, self.cache)
             slot[1], slot[2], slot[3] = graph, static, static_logits
             slot.append(self.kernels.launches - launches)
