@@ -64,8 +64,10 @@ def cmd_completion(args) -> int:
                 rid = r.request_id
                 toks = r.output if hasattr(r, "output") else r.token_ids
                 for t in toks[shown[rid]:]:
+                    if t < 0:               # sampled on the device, not read yet (steps overlap): next time
+                        break
                     print(json.dumps({"id": rid, "token": t}), flush=True)
-                shown[rid] = len(toks)
+                    shown[rid] += 1
     for rid in ids:
         r = results[rid]
         print(json.dumps({"id": rid, "prompt_tokens": r.prompt_tokens, "completion_tokens": r.completion_tokens,

@@ -138,3 +138,22 @@ def test_overlapped_steps_give_the_same_tokens_on_the_gpu(model_dirs, tiny_confi
     eng = Engine(d, dtype="float32", kv_page_size=page, kv_num_pages=128, kv_max_batch=8)
     got = eng.generate([prompts[1]], params[1], max_tokens=40, eos_token_id=stop)[0]
     assert got.token_ids == cut and got.finish_reason == "stop"
+
+
+def test_command_line_streams_the_tokens_it_reports(model_dirs):
+    """`inferctl completion --stream`: one line per token as it becomes known, then the result;
+    the streamed ids are the result's ids (no placeholder of a token not yet read)."""
+    import json
+    import subprocess
+    import sys
+    d, _ = model_dirs["B"]
+    proc = subprocess.run([sys.executable, str(helpers.ROOT / "bin" / "inferctl"), "completion", "--model", str(d),
+                           "--prompt", "5 17 3 250 9", "--max-tokens", "9", "--temperature", "0.8", "--top-p", "0.9",
+                           "--seed", "11", "--stream", "--kv-page-size", "8"],
+                          capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    lines = [json.loads(x) for x in proc.stdout.splitlines() if x.startswith("{")]
+    streamed = [x["token"] for x in lines if "token" in x]
+    final = [x for x in lines if "token_ids" in x]
+    assert len(final) == 1 and final[0]["completion_tokens"] == 9
+    assert streamed == final[0]["token_ids"] and all(t >= 0 for t in streamed)
