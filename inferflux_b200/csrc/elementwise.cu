@@ -32,6 +32,23 @@ __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict_
 // place) and the norm is taken of the sum.  ADD = 2: the delta arrives as float32
 // partial sums [splits, rows, hidden] of a K-split matrix product; they are added
 // in split order, so the result does not depend on timing.  One block per row.
+// Four consecutive elements of a row of T as floats, through one load or store.
+__device__ __forceinline__ float4 load4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 load4(const __nv_bfloat16* p) {
+  const uint2 raw = *reinterpret_cast<const uint2*>(p);
+  const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+  const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+  return make_float4(a.x, a.y, b.x, b.y);
+}
+__device__ __forceinline__ void store4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void store4(__nv_bfloat16* p, float4 v) {
+  __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+  uint2 raw;
+  raw.x = *reinterpret_cast<uint32_t*>(&a);
+  raw.y = *reinterpret_cast<uint32_t*>(&b);
+  *reinterpret_cast<uint2*>(p) = raw;
+}
+
 template <typename T, int ADD>
 __global__ void rmsnorm_kernel(float* __restrict__ x, const void* __restrict__ delta_raw,
                                const float* __restrict__ w, T* __restrict__ out, int hidden, float eps,
@@ -44,23 +61,38 @@ __global__ void rmsnorm_kernel(float* __restrict__ x, const void* __restrict__ d
   const T* dr = ADD == 1 ? reinterpret_cast<const T*>(delta_raw) + row * hidden : nullptr;
   const float* pr = ADD == 2 ? reinterpret_cast<const float*>(delta_raw) + row * hidden : nullptr;
   T* o = out + row * hidden;
-  const bool vec = (hidden & 3) == 0;                    // rows start 16-byte aligned then
+  const bool vec = (hidden & 3) == 0;                    // rows start 16-byte aligned then (8-byte for bfloat16)
+  constexpr int KEEP = 4;                                // the row's elements stay in registers between the passes
+  float4 keep[KEEP];
   float ss = 0.0f;
-  if (vec) {
-    for (int i = threadIdx.x * 4; i < hidden; i += blockDim.x * 4) {
-      float4 v = *reinterpret_cast<const float4*>(xr + i);
-      if (ADD == 1) {
-        v.x += to_f32(dr[i]); v.y += to_f32(dr[i + 1]); v.z += to_f32(dr[i + 2]); v.w += to_f32(dr[i + 3]);
-        *reinterpret_cast<float4*>(xr + i) = v;
-      } else if (ADD == 2) {
-        float4 d = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (int s = 0; s < num_splits; ++s) {
-          const float4 p = *reinterpret_cast<const float4*>(pr + (size_t)s * split_stride + i);
-          d.x += p.x; d.y += p.y; d.z += p.z; d.w += p.w;
-        }
-        v.x += d.x; v.y += d.y; v.z += d.z; v.w += d.w;
-        *reinterpret_cast<float4*>(xr + i) = v;
+  auto take = [&](int i) -> float4 {                     // x (+ delta) at columns i .. i + 3, written back
+    float4 v = *reinterpret_cast<const float4*>(xr + i);
+    if (ADD == 1) {
+      const float4 d = load4(dr + i);
+      v.x += d.x; v.y += d.y; v.z += d.z; v.w += d.w;
+      *reinterpret_cast<float4*>(xr + i) = v;
+    } else if (ADD == 2) {
+      float4 d = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int s = 0; s < num_splits; ++s) {
+        const float4 p = *reinterpret_cast<const float4*>(pr + (size_t)s * split_stride + i);
+        d.x += p.x; d.y += p.y; d.z += p.z; d.w += p.w;
       }
+      v.x += d.x; v.y += d.y; v.z += d.z; v.w += d.w;
+      *reinterpret_cast<float4*>(xr + i) = v;
+    }
+    return v;
+  };
+  const int step4 = blockDim.x * 4;
+  if (vec) {
+#pragma unroll
+    for (int c = 0; c < KEEP; ++c) {
+      const int i = threadIdx.x * 4 + c * step4;
+      keep[c] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (i < hidden) keep[c] = take(i);
+      ss += keep[c].x * keep[c].x + keep[c].y * keep[c].y + keep[c].z * keep[c].z + keep[c].w * keep[c].w;
+    }
+    for (int i = threadIdx.x * 4 + KEEP * step4; i < hidden; i += step4) {
+      const float4 v = take(i);
       ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
     }
   } else {
@@ -81,14 +113,16 @@ __global__ void rmsnorm_kernel(float* __restrict__ x, const void* __restrict__ d
   ss = block_sum(ss, scratch);
   const float r = rsqrtf(ss / (float)hidden + eps);
   if (vec) {
-    for (int i = threadIdx.x * 4; i < hidden; i += blockDim.x * 4) {
-      const float4 v = *reinterpret_cast<const float4*>(xr + i);
+    auto put = [&](int i, float4 v) {
       const float4 wv = *reinterpret_cast<const float4*>(w + i);
-      o[i] = from_f32<T>(v.x * r * wv.x);
-      o[i + 1] = from_f32<T>(v.y * r * wv.y);
-      o[i + 2] = from_f32<T>(v.z * r * wv.z);
-      o[i + 3] = from_f32<T>(v.w * r * wv.w);
+      store4(o + i, make_float4(v.x * r * wv.x, v.y * r * wv.y, v.z * r * wv.z, v.w * r * wv.w));
+    };
+#pragma unroll
+    for (int c = 0; c < KEEP; ++c) {
+      const int i = threadIdx.x * 4 + c * step4;
+      if (i < hidden) put(i, keep[c]);
     }
+    for (int i = threadIdx.x * 4 + KEEP * step4; i < hidden; i += step4) put(i, *reinterpret_cast<const float4*>(xr + i));
   } else {
     for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = from_f32<T>(xr[i] * r * w[i]);
   }
