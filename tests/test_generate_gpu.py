@@ -157,3 +157,51 @@ def test_command_line_streams_the_tokens_it_reports(model_dirs):
     final = [x for x in lines if "token_ids" in x]
     assert len(final) == 1 and final[0]["completion_tokens"] == 9
     assert streamed == final[0]["token_ids"] and all(t >= 0 for t in streamed)
+
+
+def test_many_requests_with_every_kind_of_sampling_twice(model_dirs, tiny_configs):
+    """Sixty requests of random lengths and sampling settings (greedy, temperature, top-k, top-p, min-p,
+    penalties, stop tokens) through a pool so small that requests are preempted, with overlapped steps:
+    every request finishes, every page comes back, and a second run draws the same tokens."""
+    import random
+    from inferflux_b200 import Engine, SamplingParams
+    cfg, page = tiny_configs["E"]
+    d, _ = model_dirs["E"]
+    rng = random.Random(7)
+    jobs = []
+    for i in range(60):
+        prompt = [rng.randrange(cfg.vocab_size) for _ in range(rng.choice([1, 2, 5, 17, 40, 90, 150]))]
+        kind = i % 6
+        sp = [SamplingParams(temperature=0.0),
+              SamplingParams(temperature=0.9, seed=100 + i),
+              SamplingParams(temperature=0.7, top_k=20, seed=100 + i),
+              SamplingParams(temperature=1.1, top_p=0.8, min_p=0.02, seed=100 + i),
+              SamplingParams(temperature=0.8, repetition_penalty=1.3, frequency_penalty=0.2, seed=100 + i),
+              SamplingParams(temperature=0.0, presence_penalty=0.5)][kind]
+        jobs.append((prompt, sp, rng.choice([1, 3, 12, 30]), rng.randrange(cfg.vocab_size) if i % 4 == 0 else None))
+
+    def run():
+        eng = Engine(d, dtype="bfloat16", kv_page_size=page, kv_num_pages=40, kv_max_batch=12, kv_max_seq=256,
+                     max_batch_size=12, max_batch_tokens=96, chunked_prefill_tokens=48)
+        ids = [eng.add_request(p, sp, max_tokens=m, eos_token_id=eos) for p, sp, m, eos in jobs]
+        done, guard = {}, 0
+        while eng.has_unfinished():
+            for r in eng.step():
+                done[r.request_id] = r
+            guard += 1
+            assert guard < 5000, "the engine does not finish"
+        assert not eng.runner.cache.live_requests()
+        g0 = eng.runner.cache.stats()["groups"][0]
+        assert g0["free"] == g0["pages"]
+        eng.kernels.check_errors()
+        return [(done[i].token_ids, done[i].finish_reason) for i in ids], eng.stats.preemptions
+
+    first, preemptions = run()
+    second, _ = run()
+    assert first == second
+    assert preemptions > 0, "the pool was large enough that nothing was preempted"
+    for (toks, reason), (_p, _sp, m, eos) in zip(first, jobs):
+        assert 1 <= len(toks) <= m and all(0 <= t < cfg.vocab_size for t in toks)
+        assert reason in ("length", "stop")
+        if reason == "stop":
+            assert toks[-1] == eos
