@@ -146,7 +146,8 @@ class Qwen2Config:
                 "head_dim": self.head_dim,
                 "window": self.window_of_layer(i),
                 "position": rope,
-                "qkv_bias": "if_present",
+                "qkv_bias": "if_present",            # files decide by tensor presence
+                "invent_bias": self.qkv_bias,        # random-weights mode decides by this
                 "scale": None,                       # 1 / sqrt(head_dim)
             })
             layers.append(LayerSpec(prefix=f"model.layers.{i}.", block=PartSpec("prenorm"),

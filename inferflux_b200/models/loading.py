@@ -37,17 +37,14 @@ def random_model(config, seed=0, dtype="bfloat16", device="cuda", std=0.02, norm
     dtype = parse_dtype(dtype)
     model = Model(config.to_plan())
     store = torch.float32 if dtype == torch.float32 else torch.bfloat16
-    expected = model.expected_tensors()
     # Part by part, so that at most one part's unpacked tensors exist beside the model.
     model.dtype, model.device = dtype, torch.device(device)
     for prefix, part in model.named_parts():
         own_specs = {prefix + n: s for n, s in part.param_specs().items()}
-        made = random_tensors(own_specs, seed, dtype=store, device=device, std=std, norm_jitter=norm_jitter,
-                              include_optional=bool(getattr(config, "qkv_bias", True)))
+        made = random_tensors(own_specs, seed, dtype=store, device=device, std=std, norm_jitter=norm_jitter)
         own = {n[len(prefix):]: t for n, t in made.items()}
         if part is model.lm_head:
             part.load(own, dtype, device, tied_table=model.embedding.table)
         else:
             part.load(own, dtype, device)
-    del expected
     return model

@@ -25,7 +25,8 @@ from .base import KVCacheSpec, Mixer, build_part, register_part
 class Attention(Mixer):
     """params: hidden_size, num_heads, num_kv_heads, head_dim, window (None or int),
     position (a PartSpec of role `position`, or None), qkv_bias (True, False or
-    "if_present"), scale (None for 1/sqrt(head_dim))."""
+    "if_present"), invent_bias (with "if_present": whether random-weights mode makes
+    the biases up; default True), scale (None for 1/sqrt(head_dim))."""
 
     takes_scaled_rows = True          # h goes only into the stacked projection
 
@@ -42,6 +43,7 @@ class Attention(Mixer):
         self.window = None if p.get("window") is None else int(p["window"])
         self.scale = float(p["scale"]) if p.get("scale") is not None else 1.0 / math.sqrt(self.d)
         self.qkv_bias = p.get("qkv_bias", "if_present")
+        self.invent_bias = bool(p.get("invent_bias", True))
         pos = p.get("position")
         self.position = build_part("position", pos) if pos is not None else None
         self.w_qkv = self.b_qkv = self.w_o = None
@@ -60,9 +62,8 @@ class Attention(Mixer):
         }
         if self.qkv_bias is not False:
             optional = self.qkv_bias == "if_present"
-            specs["q_proj.bias"] = TensorSpec((q,), optional=optional)
-            specs["k_proj.bias"] = TensorSpec((kv,), optional=optional)
-            specs["v_proj.bias"] = TensorSpec((kv,), optional=optional)
+            for n, size in (("q", q), ("k", kv), ("v", kv)):
+                specs[n + "_proj.bias"] = TensorSpec((size,), optional=optional, invent=self.invent_bias)
         return specs
 
     def load(self, tensors, dtype, device):

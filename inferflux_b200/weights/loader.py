@@ -27,6 +27,7 @@ class TensorSpec:
     init: str = "normal"        # how random-weights mode fills it: normal | ones | zeros
     optional: bool = False      # may be absent from the file (the part then does without it)
     ignored: bool = False       # may be present but is not used (e.g. lm_head.weight of a tied model)
+    invent: bool = True         # an optional tensor: whether random-weights mode makes it up
 
 
 class WeightError(ValueError):
