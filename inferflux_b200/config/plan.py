@@ -22,21 +22,50 @@ class PartSpec:
 
 
 @dataclass(frozen=True)
+class SubPart:
+    """One part of a layer: its role (mixer, ffn, norm, ...), what it is, and the
+    tensor-name infix of its weights below the layer's prefix."""
+    role: str
+    spec: PartSpec
+    infix: str = ""
+
+
+@dataclass(frozen=True)
 class LayerSpec:
-    """One layer: a block arrangement around a mixer and a feed-forward."""
+    """One layer: a block arrangement and the parts it arranges, by the names the
+    block kind gives them.  Which parts a layer has is the block kind's business: a
+    pre-norm block has `norm_mixer`, `mixer`, `norm_ffn`, `ffn`; another kind may have
+    four norms and no feed-forward."""
     prefix: str                 # tensor-name prefix of this layer's weights
     block: PartSpec             # arrangement (e.g. pre-norm residual block)
-    mixer: PartSpec
-    ffn: PartSpec
-    norm_mixer: PartSpec        # norm in front of the mixer
-    norm_ffn: PartSpec          # norm in front of the feed-forward
-    # tensor-name infixes of the four parts below `prefix`
-    names: Dict[str, str] = field(default_factory=lambda: {
-        "mixer": "self_attn.", "ffn": "mlp.",
-        "norm_mixer": "input_layernorm.", "norm_ffn": "post_attention_layernorm."})
+    parts: Dict[str, SubPart] = field(default_factory=dict)
 
     def __hash__(self):
-        return hash((self.prefix, self.block, self.mixer, self.ffn, self.norm_mixer, self.norm_ffn))
+        return hash((self.prefix, self.block, tuple(sorted((n, p.role, p.spec, p.infix) for n, p in self.parts.items()))))
+
+    def __getattr__(self, name):            # layer.mixer, layer.norm_ffn, ...: the part's PartSpec
+        parts = object.__getattribute__(self, "parts")
+        if name in parts:
+            return parts[name].spec
+        raise AttributeError(name)
+
+
+_PRENORM_INFIXES = {"mixer": "self_attn.", "ffn": "mlp.", "norm_mixer": "input_layernorm.",
+                    "norm_ffn": "post_attention_layernorm."}
+
+
+def prenorm_layer(prefix: str, mixer: PartSpec, ffn: PartSpec, norm_mixer: PartSpec, norm_ffn: PartSpec,
+                  names: Optional[Dict[str, str]] = None, block: Optional[PartSpec] = None) -> LayerSpec:
+    """The usual layer: x += mixer(norm(x)); x += ffn(norm(x)).  `names` overrides the
+    tensor-name infixes of the four parts (default: the HF names of a Llama-style layer)."""
+    infix = dict(_PRENORM_INFIXES)
+    infix.update(names or {})
+    return LayerSpec(prefix, block or PartSpec("prenorm"), {
+        "norm_mixer": SubPart("norm", norm_mixer, infix["norm_mixer"]),
+        "mixer": SubPart("mixer", mixer, infix["mixer"]),
+        "norm_ffn": SubPart("norm", norm_ffn, infix["norm_ffn"]),
+        "ffn": SubPart("ffn", ffn, infix["ffn"]),
+    })
 
 
 @dataclass(frozen=True)

@@ -16,7 +16,7 @@ from __future__ import annotations
 from dataclasses import dataclass, asdict
 from typing import Optional
 
-from .plan import LayerSpec, ModelPlan, PartSpec, default_schedule
+from .plan import ModelPlan, PartSpec, default_schedule, prenorm_layer
 from .registry import ConfigError, register_architecture
 
 _REQUIRED = ("hidden_size", "num_hidden_layers", "num_attention_heads", "intermediate_size", "vocab_size")
@@ -109,6 +109,11 @@ class Qwen2Config:
                               f"multiple of num_key_value_heads {self.num_key_value_heads}")
         if self.head_dim % 2:
             raise ConfigError(f"Qwen2 config: head_dim {self.head_dim} must be even for the rotation")
+        from ..parts.attention import Attention          # late: parts read the plan classes of this package
+        try:
+            Attention.check_head_dim(self.head_dim)
+        except ValueError as e:
+            raise ConfigError(f"Qwen2 config: {e}") from None
         if not (self.rms_norm_eps > 0):
             raise ConfigError(f"Qwen2 config: rms_norm_eps must be positive, got {self.rms_norm_eps}")
         if not (self.rope_theta > 0):
@@ -150,8 +155,7 @@ class Qwen2Config:
                 "invent_bias": self.qkv_bias,        # random-weights mode decides by this
                 "scale": None,                       # 1 / sqrt(head_dim)
             })
-            layers.append(LayerSpec(prefix=f"model.layers.{i}.", block=PartSpec("prenorm"),
-                                    mixer=mixer, ffn=ffn, norm_mixer=norm, norm_ffn=norm))
+            layers.append(prenorm_layer(f"model.layers.{i}.", mixer, ffn, norm, norm))
         plan = ModelPlan(
             architecture=self.architecture,
             hidden_size=self.hidden_size,

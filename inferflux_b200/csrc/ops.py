@@ -358,6 +358,24 @@ class CudaKernels:
         return out
 
     # --------------------------------------------------------------- attention
+    PREFILL_TILE = 256         # query rows per work item of the prompt-portion attention kernels
+
+    def attention_sections(self, ctx):
+        """Work lists of the attention kernels for one step, from the step's spans:
+        attn.decode_rows[D] (flat indices of spans of one token), attn.decode_meta[D,4] (flat index,
+        position, slot, 0: what the decode kernel needs of a token, in one 16-byte load),
+        attn.prefill_tiles[P,4] (request, first flat row, rows, first position) for longer spans."""
+        rows, meta, tiles, base = [], [], [], 0
+        for r, ((start, n), slot) in enumerate(zip(ctx.spans, ctx.slots_host)):
+            if n == 1:
+                rows.append(base)
+                meta.extend((base, start, int(slot), 0))
+            else:
+                for off in range(0, n, self.PREFILL_TILE):
+                    tiles.extend((r, base + off, min(self.PREFILL_TILE, n - off), start + off))
+            base += n
+        return {"attn.decode_rows": rows, "attn.decode_meta": meta, "attn.prefill_tiles": tiles}
+
     def rope_append(self, qkv, bias, rotary, nq, nkv, d, ctx, cache):
         """`qkv`: the stacked projections [T, (nq + 2 nkv) d] as a tensor or a PartialSum."""
         partial, splits = None, 0
@@ -400,31 +418,33 @@ class CudaKernels:
         win = 0 if window is None else int(window)
         common = (cache.page_size, table.shape[1], kv.shape[0], win, ctypes.c_float(scale))
         tiled = q.dtype == torch.bfloat16 and bool(self.lib.ifx_attention_mma_supports(d))
+        tiles, num_tiles = ctx.extra["attn.prefill_tiles"], ctx.extra_len["attn.prefill_tiles"] // 4
+        decode_rows, decode_meta = ctx.extra["attn.decode_rows"], ctx.extra["attn.decode_meta"]
         if not tiled:
             self._attention_generic(q, kv, table, ctx, None, T, out, nq, nkv, d, common)
             return out
-        if ctx.num_prefill_tiles and self.tensor_core_prefill and self.lib.ifx_attention_prefill_tcgen05_supports(
+        if num_tiles and self.tensor_core_prefill and self.lib.ifx_attention_prefill_tcgen05_supports(
                 d, cache.page_size):
             _check(self.lib.ifx_attention_prefill_tcgen05(
-                _ptr(q), T, _ptr(kv), _ptr(table), _ptr(ctx.prefill_tiles), _ptr(ctx.req_slot), _ptr(out),
-                ctx.num_prefill_tiles, nq, nkv, d, *common, _ptr(self.error_flag), _stream()),
+                _ptr(q), T, _ptr(kv), _ptr(table), _ptr(tiles), _ptr(ctx.req_slot), _ptr(out),
+                num_tiles, nq, nkv, d, *common, _ptr(self.error_flag), _stream()),
                 "attention (prompt portions, tcgen05)")
             self.launches += 1
-        elif ctx.num_prefill_tiles:
+        elif num_tiles:
             _check(self.lib.ifx_attention_prefill_bf16(
-                _ptr(q), _ptr(kv), _ptr(table), _ptr(ctx.prefill_tiles), _ptr(ctx.req_slot), _ptr(out),
-                ctx.num_prefill_tiles, nq, nkv, d, *common, int(ctx.max_kv_len), _ptr(self.error_flag), _stream()),
+                _ptr(q), _ptr(kv), _ptr(table), _ptr(tiles), _ptr(ctx.req_slot), _ptr(out),
+                num_tiles, nq, nkv, d, *common, int(ctx.max_kv_len), _ptr(self.error_flag), _stream()),
                 "attention (prompt portions)")
             self.launches += 1
-        n = ctx.num_decode_rows
+        n = ctx.extra_len["attn.decode_rows"]
         if n:
             if nq // nkv > 16:
-                self._attention_generic(q, kv, table, ctx, ctx.decode_rows, n, out, nq, nkv, d, common)
+                self._attention_generic(q, kv, table, ctx, decode_rows, n, out, nq, nkv, d, common)
                 return out
             max_keys = int(ctx.max_kv_len if not win else min(win, ctx.max_kv_len))
             splits = self.decode_splits(n, nkv, max_keys, int(self.lib.ifx_attention_decode_max_splits(d, cache.page_size)))
             _check(self.lib.ifx_attention_decode_bf16(
-                _ptr(q), _ptr(kv), _ptr(table), _ptr(ctx.decode_meta), _ptr(out), n, nq, nkv, d, *common, splits,
+                _ptr(q), _ptr(kv), _ptr(table), _ptr(decode_meta), _ptr(out), n, nq, nkv, d, *common, splits,
                 max_keys, _ptr(self.error_flag), _stream()), "attention (decoded tokens)")
             self.launches += 1
         return out

@@ -16,9 +16,6 @@ from typing import Dict, Hashable, List, Optional, Sequence
 
 import torch
 
-PREFILL_TILE = 256         # query rows per work item of the prompt-portion attention kernel
-
-
 @dataclass
 class StepEntry:
     """A request's next tokens and the places among them whose logits are wanted."""
@@ -34,10 +31,9 @@ class StepContext:
     batch), cu_seqlens[R+1] (span boundaries in the flat arrays), kv_lens[R]
     (tokens stored once the step is done), req_slot[R] (row of the block tables and
     of the state tensors), logit_rows[W] (flat token indices whose logits are
-    wanted), decode_rows[D] (flat indices of spans of one token), decode_meta[D,4]
-    (flat index, position, slot, 0: what the decode attention kernel needs of a token,
-    in one 16-byte load), prefill_tiles[P,4] (request, first flat row, rows, first
-    position) for longer spans.
+    wanted).  What else a kind of part wants on the device for a step (work lists of
+    its kernels, say) it declares through `Part.step_sections`; those arrays travel in
+    the same copy and are found in `extra[name]`, their lengths in `extra_len[name]`.
     """
 
     def __init__(self, kernels, dtype, device):
@@ -47,8 +43,6 @@ class StepContext:
         self.num_tokens = 0
         self.num_requests = 0
         self.num_logit_rows = 0
-        self.num_decode_rows = 0
-        self.num_prefill_tiles = 0
         self.max_kv_len = 0
         self.max_span = 0
         # host copies, for parts written in plain torch and for tests
@@ -56,17 +50,20 @@ class StepContext:
         self.kv_lens_host: List[int] = []
         self.slots_host: List[int] = []
         self.request_ids: List[Hashable] = []
+        self.extra: Dict[str, torch.Tensor] = {}
+        self.extra_len: Dict[str, int] = {}
 
     @classmethod
     def build(cls, kernels, dtype, device, entries: Sequence[StepEntry], starts: Sequence[int],
               slots: Sequence[int], table_updates: Sequence[Sequence[tuple]] = (),
-              relay: Optional[Sequence[tuple]] = None):
+              relay: Optional[Sequence[tuple]] = None, providers: Sequence = ()):
         """Pack the arrays for `entries`; `starts[i]` is how many tokens request i
         already holds, `slots[i]` its slot, `table_updates[g]` the block-table
-        entries of group g that changed since the last step."""
+        entries of group g that changed since the last step; `providers` are parts
+        whose `step_sections(ctx)` adds int32 lists of their own."""
         ctx = cls(kernels, dtype, device)
         token_ids, positions, token_req, cu, kv_lens = [], [], [], [0], []
-        logit_rows, decode_rows, decode_meta, tiles = [], [], [], []
+        logit_rows = []
         for r, (e, start) in enumerate(zip(entries, starts)):
             n = len(e.tokens)
             if n == 0:
@@ -81,18 +78,10 @@ class StepContext:
                 if not 0 <= int(w) < n:
                     raise ValueError(f"request {e.request_id!r}: wanted place {w} is outside its {n} tokens")
                 logit_rows.append(base + int(w))
-            if n == 1:
-                decode_rows.append(base)
-                decode_meta.extend((base, start, int(slots[r]), 0))
-            else:
-                for off in range(0, n, PREFILL_TILE):
-                    tiles.append((r, base + off, min(PREFILL_TILE, n - off), start + off))
             ctx.spans.append((start, n))
         ctx.num_tokens = cu[-1]
         ctx.num_requests = len(entries)
         ctx.num_logit_rows = len(logit_rows)
-        ctx.num_decode_rows = len(decode_rows)
-        ctx.num_prefill_tiles = len(tiles)
         ctx.kv_lens_host = kv_lens
         ctx.slots_host = list(slots)
         ctx.request_ids = [e.request_id for e in entries]
@@ -102,9 +91,15 @@ class StepContext:
         sections: Dict[str, List[int]] = {
             "token_ids": token_ids, "positions": positions, "token_req": token_req,
             "cu_seqlens": cu, "kv_lens": kv_lens, "req_slot": list(slots),
-            "logit_rows": logit_rows, "decode_rows": decode_rows, "decode_meta": decode_meta,
-            "prefill_tiles": [v for t in tiles for v in t],
+            "logit_rows": logit_rows,
         }
+        ctx._extra_names = []
+        for part in providers:
+            for name, vals in part.step_sections(ctx).items():
+                if name in sections:
+                    raise ValueError(f"step section {name!r} is declared twice")
+                sections[name] = list(vals)
+                ctx._extra_names.append(name)
         for g, ups in enumerate(table_updates):
             sections[f"upd_index_{g}"] = [u[0] for u in ups]
             sections[f"upd_page_{g}"] = [u[1] for u in ups]
@@ -136,19 +131,20 @@ class StepContext:
         ctx.relay_src = dev[offsets["upd_relay_src"][0]:][:offsets["upd_relay_src"][1]]
         return ctx
 
-    _CORE = ("token_ids", "positions", "token_req", "cu_seqlens", "kv_lens", "req_slot", "logit_rows",
-             "decode_rows", "decode_meta", "prefill_tiles")
+    _CORE = ("token_ids", "positions", "token_req", "cu_seqlens", "kv_lens", "req_slot", "logit_rows")
 
     def _bind(self, buffer):
         for name in self._CORE:
             off, n = self._offsets[name]
             setattr(self, name, buffer[off:off + n])
-        self.prefill_tiles = self.prefill_tiles.view(-1, 4)
-        self.decode_meta = self.decode_meta.view(-1, 4)
+        for name in self._extra_names:
+            off, n = self._offsets[name]
+            self.extra[name] = buffer[off:off + n]
+            self.extra_len[name] = n
 
     def layout_key(self):
         """Two steps with the same key have their arrays at the same offsets."""
-        return tuple(self._offsets[n] for n in self._CORE)
+        return tuple(self._offsets[n] for n in self._CORE) + tuple((n, self._offsets[n]) for n in self._extra_names)
 
     def core_buffer(self):
         return self._buffer[:self._core_len]

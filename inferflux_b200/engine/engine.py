@@ -114,7 +114,19 @@ class Engine:
         item = torch.empty(0, dtype=self.dtype).element_size()
         return sum(2 * kv.num_kv_heads * kv.head_dim * item for kv, _st in self.model.cache_specs() if kv)
 
+    def state_bytes_per_request(self) -> int:
+        """Bytes of fixed-size state one request slot takes over all caches."""
+        total = 0
+        for _kv, st in self.model.cache_specs():
+            if st is not None:
+                n = torch.empty(0, dtype=st.dtype).element_size()
+                for s in st.shape:
+                    n *= int(s)
+                total += n
+        return total
+
     def _plan_pages(self, page_size, max_seqs, max_seq, budget_mb, ratio) -> int:
+        """Pages that fit the budget once the state slots of `max_seqs` requests are paid for."""
         per_page = max(1, self.bytes_per_token() * page_size)
         if budget_mb is not None:
             budget = int(budget_mb * 1024 * 1024)
@@ -123,7 +135,7 @@ class Engine:
             budget = int(free * ratio)
         else:
             budget = 64 * 1024 * 1024
-        pages = budget // per_page
+        pages = max(0, budget - max_seqs * self.state_bytes_per_request()) // per_page
         most = max_seqs * (-(-max_seq // page_size))          # more than this can never be in use
         return int(max(1, min(pages, most)))
 

@@ -136,7 +136,8 @@ class ModelRunner:
             slots.append(cache.slot(e.request_id))
 
         ctx = StepContext.build(self.kernels, self.dtype, self.device, entries, starts, slots,
-                                cache.drain_table_updates(), relay[0] if relay else None)
+                                cache.drain_table_updates(), relay[0] if relay else None,
+                                providers=getattr(self.model, "section_providers", ()))
         for group, (index, page) in zip(cache.groups, ctx.table_updates):
             self.kernels.scatter_i32(group.table, index, page)
         ctx.relay_ids = relay[1] if relay else None

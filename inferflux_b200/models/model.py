@@ -17,20 +17,21 @@ from ..weights.loader import TensorSpec
 
 
 class Layer:
+    """A layer's parts, built from its spec, and the block that arranges them."""
+
     def __init__(self, spec):
         self.spec = spec
-        self.mixer = build_part("mixer", spec.mixer)
-        self.ffn = build_part("ffn", spec.ffn)
-        self.norm_mixer = build_part("norm", spec.norm_mixer)
-        self.norm_ffn = build_part("norm", spec.norm_ffn)
-        self.block = build_part("block", spec.block, self.mixer, self.ffn, self.norm_mixer, self.norm_ffn)
+        self.parts = {name: build_part(sub.role, sub.spec) for name, sub in spec.parts.items()}
+        self.block = build_part("block", spec.block, self.parts)
+
+    def __getattr__(self, name):            # layer.mixer, layer.ffn, ...: the built part
+        parts = self.__dict__.get("parts", {})
+        if name in parts:
+            return parts[name]
+        raise AttributeError(name)
 
     def named_parts(self):
-        names = self.spec.names
-        return [(self.spec.prefix + names["norm_mixer"], self.norm_mixer),
-                (self.spec.prefix + names["mixer"], self.mixer),
-                (self.spec.prefix + names["norm_ffn"], self.norm_ffn),
-                (self.spec.prefix + names["ffn"], self.ffn)]
+        return [(self.spec.prefix + sub.infix, self.parts[name]) for name, sub in self.spec.parts.items()]
 
 
 class Model:
@@ -43,6 +44,14 @@ class Model:
         self.lm_head = build_part("lm_head", plan.lm_head)
         self.dtype = None
         self.device = None
+        # one part of every class that wants arrays of its own in a step's metadata
+        from ..parts.base import Part
+        seen = {}
+        for _prefix, part in self.named_parts():
+            for p in [part] + list(getattr(part, "sub_parts", lambda: [])()):
+                if type(p).step_sections is not Part.step_sections:
+                    seen.setdefault(type(p), p)
+        self.section_providers = list(seen.values())
 
     # ------------------------------------------------------------------- tensors
     def named_parts(self):
@@ -73,12 +82,12 @@ class Model:
 
     # ------------------------------------------------------------------ cache needs
     def cache_specs(self):
-        """Per cache index: (KVCacheSpec or None, StateSpec or None), from the mixer
-        of the layer that writes that cache."""
+        """Per cache index: (KVCacheSpec or None, StateSpec or None), from the part
+        that the block of the writing layer names as the one that stores."""
         out = []
         for c in range(self.plan.num_caches):
-            mixer = self.layers[self.plan.cache_owner_layer(c)].mixer
-            out.append((mixer.cache_spec(), mixer.state_spec()))
+            part = self.layers[self.plan.cache_owner_layer(c)].block.cache_part()
+            out.append((None, None) if part is None else (part.cache_spec(), part.state_spec()))
         return out
 
     # --------------------------------------------------------------------- forward

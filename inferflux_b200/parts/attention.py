@@ -30,6 +30,12 @@ class Attention(Mixer):
 
     takes_scaled_rows = True          # h goes only into the stacked projection
 
+    @staticmethod
+    def check_head_dim(d: int) -> None:
+        """The attention kernels (tiled or per-token) take head sizes that are multiples of 8 up
+        to 256; anything else is refused when the model is planned, not at the first step."""
+        if d <= 0 or d % 8 or d > 256:
+            raise ValueError(f"attention: head size {d} is not supported (multiples of 8 up to 256)")
 
     def __init__(self, spec):
         super().__init__(spec)
@@ -38,6 +44,7 @@ class Attention(Mixer):
         self.nq = int(p["num_heads"])
         self.nkv = int(p["num_kv_heads"])
         self.d = int(p["head_dim"])
+        self.check_head_dim(self.d)
         if self.nq % self.nkv:
             raise ValueError(f"attention: {self.nq} heads are not a multiple of {self.nkv} kv heads")
         self.window = None if p.get("window") is None else int(p["window"])
@@ -80,6 +87,11 @@ class Attention(Mixer):
             self.b_qkv = torch.cat(parts).contiguous()      # added in float32
         else:
             self.b_qkv = None
+
+    def step_sections(self, ctx):
+        """The work lists of the kernel table's attention kernels, if it has any."""
+        make = getattr(ctx.kernels, "attention_sections", None)
+        return make(ctx) if make is not None else {}
 
     # --------------------------------------------------------------------- forward
     def forward(self, h, ctx, cache):

@@ -9,7 +9,7 @@ does its work through the kernel table of the step (`ctx.kernels`).
     PositionEncoding  rotary() -> RotaryTable or None
     Mixer             cache_spec() / state_spec(); forward(h, ctx, cache) -> y
     FeedForward       forward(h, ctx) -> y
-    Block             forward(x, pending, ctx, cache) -> (x, pending)
+    Block             sub_parts (name -> role); forward(x, pending, ctx, cache) -> (x, pending)
 
 `x` is the float32 residual stream [tokens, hidden]; `h` and `y` are in the dtype
 the run computes in.  `pending` is a delta that has not been added to `x` yet, so
@@ -80,6 +80,16 @@ class Part:
         """Take the tensors named by `param_specs` (absent optional ones are left
         out of `tensors`) and keep them in the form the kernels want."""
 
+    def step_sections(self, ctx) -> Dict[str, list]:
+        """Int32 lists that parts of this class want on the device for the step `ctx`
+        describes (`ctx.spans`, `ctx.slots_host`, `ctx.kv_lens_host` are set): work
+        lists of its kernels, for instance.  They travel in the step's one metadata
+        copy and are found in `ctx.extra[name]` (a flat int32 device array) with
+        `ctx.extra_len[name]`; names carry the class's own prefix.  Called once per
+        step on one part of each class, so the lists may depend on the step only, not
+        on the part's parameters."""
+        return {}
+
 
 class Norm(Part):
     def forward(self, x: torch.Tensor, delta: Optional[torch.Tensor], ctx, lazy: bool = False) -> torch.Tensor:
@@ -110,11 +120,26 @@ class FeedForward(Part):
 
 
 class Block(Part):
-    """Arrangement of two norms, a mixer and a feed-forward around the residual."""
+    """An arrangement of parts around the residual stream.  A block kind says which
+    parts it arranges (`sub_parts`: name -> role); the layer's spec must bring exactly
+    those, and `forward` finds them under their names as attributes."""
 
-    def __init__(self, spec, mixer: Mixer, ffn: FeedForward, norm_mixer: Norm, norm_ffn: Norm):
+    sub_parts: Dict[str, str] = {}
+
+    def __init__(self, spec, parts: Dict[str, Part]):
         super().__init__(spec)
-        self.mixer, self.ffn, self.norm_mixer, self.norm_ffn = mixer, ffn, norm_mixer, norm_ffn
+        missing = sorted(set(self.sub_parts) - set(parts))
+        extra = sorted(set(parts) - set(self.sub_parts))
+        if missing or extra:
+            raise ValueError(f"block {spec.kind!r} arranges {sorted(self.sub_parts)}; the layer lacks {missing} "
+                             f"and brings {extra} besides")
+        self.parts = dict(parts)
+        for name, part in parts.items():
+            setattr(self, name, part)
+
+    def cache_part(self) -> Optional[Part]:
+        """The part whose `cache_spec()` / `state_spec()` say what this layer stores (None: nothing)."""
+        return self.parts.get("mixer")
 
     def forward(self, x, pending, ctx, cache):
         raise NotImplementedError

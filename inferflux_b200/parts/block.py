@@ -9,6 +9,8 @@ from .base import Block, register_part
 
 @register_part("block", "prenorm")
 class PreNormBlock(Block):
+    sub_parts = {"norm_mixer": "norm", "mixer": "mixer", "norm_ffn": "norm", "ffn": "ffn"}
+
     def forward(self, x, pending, ctx, cache):
         h = self.norm_mixer.forward(x, pending, ctx, lazy=self.mixer.takes_scaled_rows)   # x += pending; h = norm(x)
         a = self.mixer.forward(h, ctx, cache)

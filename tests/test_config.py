@@ -93,3 +93,16 @@ def test_schedule_is_checked():
     plan.schedule = [ScheduleEntry(5, 0)]
     with pytest.raises(ValueError):
         plan.validate()
+
+
+def test_a_head_size_the_kernels_do_not_take_is_refused_when_the_config_is_read():
+    from inferflux_b200.config import ConfigError, config_from_dict
+    raw = dict(architectures=["Qwen2ForCausalLM"], hidden_size=96, num_hidden_layers=1, num_attention_heads=8,
+               num_key_value_heads=2, intermediate_size=64, vocab_size=100)
+    with pytest.raises(ConfigError, match="head size 12"):          # hidden_size / heads, no head_dim given
+        config_from_dict(raw)
+    for head_dim in (12, 20, 264, 320):
+        with pytest.raises(ConfigError, match="head size"):
+            config_from_dict(dict(raw, head_dim=head_dim))
+    for head_dim in (8, 24, 128, 256):
+        assert config_from_dict(dict(raw, head_dim=head_dim)).head_dim == head_dim

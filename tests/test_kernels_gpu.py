@@ -225,19 +225,14 @@ def make_cache_case(dtype, nkv, d, page, lens, spans, num_pages, seed, shuffle=T
     ctx.token_req = torch.tensor(token_req, dtype=torch.int32, device=DEV)
     ctx.req_slot = torch.tensor(slots, dtype=torch.int32, device=DEV)
     ctx.num_tokens = len(positions)
-    tiles, decode_rows, base = [], [], 0
-    for r, (n, s_) in enumerate(zip(lens, spans)):
-        if s_ == 1:
-            decode_rows.append(base)
-        else:
-            for off in range(0, s_, 256):
-                tiles.append([r, base + off, min(256, s_ - off), n - s_ + off])
-        base += s_
-    ctx.decode_rows = torch.tensor(decode_rows, dtype=torch.int32, device=DEV)
-    ctx.decode_meta = torch.tensor([[t, positions[t], slots[token_req[t]], 0] for t in decode_rows],
-                                   dtype=torch.int32, device=DEV).view(-1, 4)
-    ctx.prefill_tiles = torch.tensor(tiles, dtype=torch.int32, device=DEV).view(-1, 4)
-    ctx.num_decode_rows, ctx.num_prefill_tiles = len(decode_rows), len(tiles)
+    # the work lists of the attention kernels, as the kernel table makes them for a step
+    ctx.spans = [(n - s_, s_) for n, s_ in zip(lens, spans)]
+    ctx.slots_host = slots
+    from inferflux_b200.csrc import CudaKernels
+    ctx.extra, ctx.extra_len = {}, {}
+    for name, vals in CudaKernels.attention_sections(CudaKernels, ctx).items():
+        ctx.extra[name] = torch.tensor(vals, dtype=torch.int32, device=DEV)
+        ctx.extra_len[name] = len(vals)
     ctx.max_kv_len = max(lens)
     cache = CacheView(kv.to(DEV), table.to(DEV), page, None, True, 0)
     return ctx, cache, slots

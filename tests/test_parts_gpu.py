@@ -197,16 +197,16 @@ def _register_toys():
 
 
 def _toy_plan(H, V, I):
-    from inferflux_b200.config import LayerSpec, ModelPlan, PartSpec, ScheduleEntry
+    from inferflux_b200.config import ModelPlan, PartSpec, ScheduleEntry, prenorm_layer
     norm = PartSpec("rmsnorm", {"size": H, "eps": 1e-5})
     attn = PartSpec("attention", {"hidden_size": H, "num_heads": 4, "num_kv_heads": 2, "head_dim": 16, "window": None,
                                   "qkv_bias": "if_present", "scale": 0.3,
                                   "position": PartSpec("toy_scaled_rope", {"theta": 1e4, "rotary_dim": 8, "factor": 4.0})})
     swiglu = PartSpec("swiglu", {"hidden_size": H, "intermediate_size": I})
     layers = [
-        LayerSpec("model.layers.0.", PartSpec("prenorm"), attn, swiglu, norm, norm),
-        LayerSpec("model.layers.1.", PartSpec("prenorm"), PartSpec("toy_decay", {"hidden_size": H}),
-                  PartSpec("toy_routed", {"hidden_size": H, "intermediate_size": I}), norm, norm),
+        prenorm_layer("model.layers.0.", attn, swiglu, norm, norm),
+        prenorm_layer("model.layers.1.", PartSpec("toy_decay", {"hidden_size": H}),
+                      PartSpec("toy_routed", {"hidden_size": H, "intermediate_size": I}), norm, norm),
     ]
     # layer 0 runs twice (second time on a cache of its own), then the toy layer
     schedule = [ScheduleEntry(0, 0), ScheduleEntry(1, 1), ScheduleEntry(0, 2)]
@@ -293,6 +293,88 @@ def test_toy_parts_register_build_and_step(cuda_kernels):
     for make in (helpers.trace_whole, helpers.trace_portions, lambda r: helpers.trace_mixed(r, 192)):
         runner = ModelRunner(model, cuda_kernels, page_size=8, num_pages=192 // 8, max_seqs=4, cuda_graphs=True)
         assert not runner.cuda_graphs                      # a part said it cannot be captured
+        steps = make(reqs)
+        got = helpers.collect(steps, helpers.run_steps_in_process(runner, steps), V)
+        bad = helpers.first_bad(got, want, 2e-4)
+        assert bad is None, f"first wrong row (request, position, diff): {bad}"
+
+
+def test_a_block_kind_of_the_tests_own_with_four_norms_and_no_feed_forward(cuda_kernels):
+    """A block arrangement defined here, with parts under names of its own (four norms around a
+    mixer, no feed-forward), becomes a model without a change to the framework's files: the plan
+    names the parts, the block kind says which it arranges, weights are declared and made by them."""
+    from inferflux_b200.config import LayerSpec, ModelPlan, PartSpec, SubPart, default_schedule
+    from inferflux_b200.engine import ModelRunner
+    from inferflux_b200.models import Model
+    from inferflux_b200.parts import Block, register_part
+    from inferflux_b200.weights import random_tensors
+    _register_toys()
+
+    @register_part("block", "toy_sandwich")
+    class SandwichBlock(Block):
+        """x += post(mixer(pre(x)));  x += outer(inner(x))."""
+        sub_parts = {"pre": "norm", "mixer": "mixer", "post": "norm", "inner": "norm", "outer": "norm"}
+
+        def forward(self, x, pending, ctx, cache):
+            k = ctx.kernels
+            if pending is not None:
+                k.residual_add(x, pending)
+            a = k.materialize(self.mixer.forward(self.pre.forward(x, None, ctx), ctx, cache))
+            k.residual_add(x, self.post.forward(a.float(), None, ctx))
+            g = self.outer.forward(self.inner.forward(x, None, ctx).float(), None, ctx)
+            return x, g                                   # handed on unadded, like any block's last delta
+
+    H, V = 48, 200
+    attn = PartSpec("attention", {"hidden_size": H, "num_heads": 3, "num_kv_heads": 1, "head_dim": 16, "window": None,
+                                  "qkv_bias": False, "scale": None,
+                                  "position": PartSpec("rope", {"theta": 1e4, "rotary_dim": 16})})
+    def norm(eps):
+        return PartSpec("rmsnorm", {"size": H, "eps": eps})
+    layers = []
+    for i, mixer in enumerate((attn, PartSpec("toy_decay", {"hidden_size": H}))):
+        layers.append(LayerSpec(f"blocks.{i}.", PartSpec("toy_sandwich"), {
+            "pre": SubPart("norm", norm(1e-5), "n1."), "mixer": SubPart("mixer", mixer, "mix."),
+            "post": SubPart("norm", norm(1e-4), "n2."), "inner": SubPart("norm", norm(1e-3), "n3."),
+            "outer": SubPart("norm", norm(1e-2), "n4.")}))
+    with pytest.raises(ValueError, match="lacks"):           # a layer that does not bring what the block arranges
+        Model(ModelPlan("Bad", H, V, 128, PartSpec("embedding", {"vocab_size": V, "hidden_size": H}),
+                        [LayerSpec("blocks.0.", PartSpec("toy_sandwich"), {"mixer": SubPart("mixer", attn, "mix.")})],
+                        default_schedule(1), norm(1e-5), PartSpec("lm_head", {"vocab_size": V, "hidden_size": H, "tied": True})))
+    plan = ModelPlan("ToySandwich", H, V, 128, PartSpec("embedding", {"vocab_size": V, "hidden_size": H}), layers,
+                     default_schedule(2), norm(1e-5), PartSpec("lm_head", {"vocab_size": V, "hidden_size": H, "tied": True}))
+    model = Model(plan)
+    expected = model.expected_tensors()
+    assert "blocks.0.n4.weight" in expected and "blocks.1.mix.decay" in expected and not any("mlp" in n for n in expected)
+    W = random_tensors(expected, seed=8, dtype=torch.float32, std=0.1, norm_jitter=0.2)
+    W["model.embed_tokens.weight"] *= 8
+    model.load(W, torch.float32, DEV)
+
+    def oracle(toks):
+        Wd = {k: v.double() for k, v in W.items()}
+        T = len(toks)
+        x = Wd["model.embed_tokens.weight"][torch.tensor(toks)]
+        for i in range(2):
+            p = f"blocks.{i}."
+            h = plain_qwen2.rmsnorm(x, Wd[p + "n1.weight"], 1e-5)
+            if i == 0:
+                q = plain_qwen2.rope_neox(plain_qwen2.linear(h, Wd[p + "mix.q_proj.weight"]).view(T, 3, 16), torch.arange(T), 1e4)
+                k = plain_qwen2.rope_neox(plain_qwen2.linear(h, Wd[p + "mix.k_proj.weight"]).view(T, 1, 16), torch.arange(T), 1e4)
+                v = plain_qwen2.linear(h, Wd[p + "mix.v_proj.weight"]).view(T, 1, 16)
+                a = plain_qwen2.attention_gqa_causal(q, k, v).reshape(T, 48) @ Wd[p + "mix.o_proj.weight"].t()
+            else:
+                decay, s, ys = torch.sigmoid(W[p + "mix.decay"].float()).double(), torch.zeros(H, dtype=torch.float64), []
+                for t in range(T):
+                    s = decay * s + h[t]
+                    ys.append(s)
+                a = torch.stack(ys) @ Wd[p + "mix.out.weight"].t()
+            x = x + plain_qwen2.rmsnorm(a, Wd[p + "n2.weight"], 1e-4)
+            x = x + plain_qwen2.rmsnorm(plain_qwen2.rmsnorm(x, Wd[p + "n3.weight"], 1e-3), Wd[p + "n4.weight"], 1e-2)
+        return plain_qwen2.rmsnorm(x, Wd["model.norm.weight"], 1e-5) @ Wd["model.embed_tokens.weight"].t()
+
+    reqs = {f"r{i}": helpers.random_tokens(V, n, 300 + i) for i, n in enumerate([35, 50, 21])}
+    want = {rid: oracle(toks).numpy() for rid, toks in reqs.items()}
+    for make in (helpers.trace_whole, helpers.trace_portions, lambda r: helpers.trace_mixed(r, 128)):
+        runner = ModelRunner(model, cuda_kernels, page_size=8, num_pages=128 // 8, max_seqs=4)
         steps = make(reqs)
         got = helpers.collect(steps, helpers.run_steps_in_process(runner, steps), V)
         bad = helpers.first_bad(got, want, 2e-4)

@@ -145,3 +145,25 @@ def test_sharded_folder(tmp_path):
     (d / "model.safetensors.index.json").write_text(json.dumps({"weight_map": wm}))
     got = load_weights(d, expected_tensors(CFG.to_plan()))
     assert all(torch.equal(got[n], tensors[n]) for n in names)
+
+
+def test_made_up_weights_depend_on_seed_name_and_element_only():
+    from inferflux_b200.weights.random_init import counter_normal, counter_normal_numpy, tensor_key
+    a = counter_normal((7, 33), 5, "model.layers.0.mlp.up_proj.weight", 0.0, 0.02)
+    again = counter_normal((7, 33), 5, "model.layers.0.mlp.up_proj.weight", 0.0, 0.02)
+    assert torch.equal(a, again)
+    # element i is the same whatever the tensor's shape or the chunk it is made in
+    flat = counter_normal((231,), 5, "model.layers.0.mlp.up_proj.weight", 0.0, 0.02)
+    assert torch.equal(a.reshape(-1), flat)
+    k0, k1 = tensor_key(5, "model.layers.0.mlp.up_proj.weight")
+    tail = counter_normal_numpy(31, k0, k1, 0.0, 0.02, first=200)
+    assert (flat.numpy()[200:] == tail).all()
+    # another name or another seed: other values
+    assert not torch.equal(a, counter_normal((7, 33), 5, "model.layers.1.mlp.up_proj.weight", 0.0, 0.02))
+    assert not torch.equal(a, counter_normal((7, 33), 6, "model.layers.0.mlp.up_proj.weight", 0.0, 0.02))
+    big = counter_normal((400, 500), 1, "w", 0.0, 1.0).double()
+    assert abs(float(big.mean())) < 0.01 and abs(float(big.std()) - 1.0) < 0.01
+    kurt = float(((big - big.mean()) ** 4).mean() / big.var() ** 2) - 3.0
+    assert abs(kurt) < 0.05
+    # bfloat16 is the float32 value rounded once
+    assert torch.equal(counter_normal((7, 33), 5, "n", 0.0, 0.02, torch.bfloat16), counter_normal((7, 33), 5, "n", 0.0, 0.02).to(torch.bfloat16))

@@ -29,3 +29,28 @@ def test_tensors_reach_the_device_unchanged_through_small_staging_chunks(tmp_pat
         v = f.view("b.weight")
         assert torch.equal(v, tensors["b.weight"])
         del v
+
+
+def test_the_same_seed_gives_the_same_bits_on_the_host_and_on_the_device(tmp_path):
+    """`random_model` on the GPU, `write_random_model` on the host and a folder loaded back hold
+    bit-identical weights: element i of a tensor depends on (seed, name, i) alone."""
+    from inferflux_b200.config import Qwen2Config
+    from inferflux_b200.models import expected_tensors
+    from inferflux_b200.weights import SafetensorsFile, write_random_model
+    from inferflux_b200.weights.random_init import counter_normal, random_tensors
+    cfg = Qwen2Config(hidden_size=136, num_hidden_layers=2, num_attention_heads=6, num_key_value_heads=2, head_dim=64,
+                      intermediate_size=264, vocab_size=641, max_position_embeddings=128)
+    specs = expected_tensors(cfg.to_plan())
+    for dtype in (torch.bfloat16, torch.float32):
+        on_device = random_tensors(specs, seed=9, dtype=dtype, device="cuda:0", norm_jitter=0.1)
+        write_random_model(cfg, tmp_path / str(dtype), seed=9, dtype=dtype, norm_jitter=0.1)
+        with SafetensorsFile(tmp_path / str(dtype) / "model.safetensors") as f:
+            assert sorted(f.names()) == sorted(on_device)
+            for n in f.names():
+                assert torch.equal(f.tensor(n), on_device[n].cpu()), (n, dtype)
+    # a tensor of more than 2^21 elements (several host chunks), odd size, another seed and a large one
+    for seed in (0, 2 ** 40 + 17):
+        host = counter_normal((3, 1_400_001), seed, "x.weight", 0.0, 0.02, torch.float32, "cpu")
+        dev = counter_normal((3, 1_400_001), seed, "x.weight", 0.0, 0.02, torch.float32, "cuda:0")
+        assert torch.equal(host, dev.cpu())
+    assert abs(float(host.std()) - 0.02) < 2e-4 and abs(float(host.mean())) < 1e-4
