@@ -34,6 +34,9 @@ from pathlib import Path
 HERE = Path(__file__).resolve().parent
 OUT = HERE / "_ref"
 HARNESS = HERE / "ref_harness.cu"
+HOST_PROBE = HERE / "ref_host_probe.cpp"
+HOST_SOURCES = ["runtime/backends/cuda/native/safetensors_parser.cpp", "server/logging/logger.cpp"]
+HOST_HEADERS = ["runtime/backends/cuda/native/kv_cache_planner.h"]
 
 N = "runtime/backends/cuda/native/"
 SOURCES = [
@@ -115,9 +118,9 @@ def copy_sources(root: Path):
     stub.mkdir(parents=True, exist_ok=True)
     (stub / "llama.h").write_text(STUB_LLAMA_H)
     say(f"copying the model path's sources from {root}")
-    files = set(SOURCES)
+    files = set(SOURCES) | set(HOST_SOURCES) | set(HOST_HEADERS)
     with ThreadPoolExecutor(max_workers=8) as pool:
-        for deps in pool.map(lambda r: dependencies(root, r, stub), SOURCES):
+        for deps in pool.map(lambda r: dependencies(root, r, stub), SOURCES + HOST_SOURCES):
             files |= deps
     manifest = {}
     for rel in sorted(files):
@@ -156,6 +159,28 @@ def compile_all():
         raise RuntimeError(f"linking ref_harness failed:\n{p.stderr[-4000:]}")
     (OUT / "stamp.txt").write_text(stamp() + "\n")
     say(f"linked {exe}")
+    return exe
+
+
+def build_host_probe() -> Path:
+    """The host-only probe (the reference's safetensors parser and its cache-size arithmetic): g++, no GPU."""
+    exe = OUT / "ref_host_probe"
+    src = OUT / "src"
+    if exe.is_file() and exe.stat().st_mtime >= HOST_PROBE.stat().st_mtime:
+        return exe
+    if not (src / HOST_SOURCES[0]).is_file():
+        root = reference_root(None)
+        if root is None:
+            raise RuntimeError("no reference checkout and no copied sources under baseline/_ref/src")
+        copy_sources(root)
+    cxx = shutil.which("g++") or shutil.which("c++")
+    if not cxx:
+        raise RuntimeError("no C++ compiler")
+    cmd = [cxx, "-std=c++17", "-O1", "-w", f"-I{src}", f"-I{src / 'external'}", str(HOST_PROBE),
+           *[str(src / r) for r in HOST_SOURCES], "-o", str(exe), "-lpthread"]
+    p = subprocess.run(cmd, capture_output=True, text=True)
+    if p.returncode != 0:
+        raise RuntimeError(f"building ref_host_probe failed:\n{p.stderr[-3000:]}")
     return exe
 
 

@@ -1,10 +1,11 @@
 """Plain whole-sequence implementation of the Qwen2.5 dense decoder (the oracle).
 
-It rests on the reference's formulas, not on its code: the reference's model file
-(runtime/backends/cuda/native/transformer_forward.cu) cannot be compiled or
-imported on a CPU (its include chain needs the absent llama.cpp submodule and it
-has no CPU model code), so nothing here was checked against a run of it.  Each
-function cites the reference lines it restates.
+It restates the reference's formulas, each function citing the lines it restates, and
+is held to the reference's own results: tests/test_golden.py compares every function
+here, and the whole forward, with outputs of the unmodified reference code (its leaf
+host wrappers and its LlamaForwardTyped<T> model path, run once on a GPU by
+tests/golden/make_goldens.py and kept under tests/golden/).  The reference has no CPU
+model code, so it cannot be imported here.
 
 Whole sequences only: no cache, no batching, no paging.  One function per part.
 Weights are a dict name -> torch tensor with HF tensor names; the config is the
