@@ -222,6 +222,21 @@ class CacheManager:
                 req.lo[gi] = start
             req.hi[gi] = last
 
+    def release_uncommitted(self, rid) -> None:
+        """Give back the blocks that `reserve` took beyond what the committed length needs (a step
+        that reserved and then failed before `commit`)."""
+        req = self._requests[rid]
+        keep = -(-req.length // self.page_size)
+        for gi, (g, held) in enumerate(zip(self.groups, req.blocks)):
+            dead = [b for b in held if b >= keep]
+            if dead:
+                g.alloc.release([held[b] for b in dead], owner=rid)
+                for b in dead:
+                    del held[b]
+                gone = {req.slot * self.max_blocks + b for b in dead}
+                g.updates = [(i, p) for i, p in g.updates if i not in gone]     # the table never learns of them
+            req.hi[gi] = max(req.lo[gi], min(req.hi[gi], keep))
+
     def commit(self, rid, new_len: int) -> None:
         """The step has stored positions up to new_len - 1; pages that a window has
         moved past are given back."""

@@ -22,6 +22,7 @@ class StepEntry:
     request_id: Hashable
     tokens: Sequence[int]
     want: Sequence[int] = field(default_factory=list)
+    start: Optional[int] = None       # where the caller believes these tokens begin; checked against the cache
 
 
 class StepContext:

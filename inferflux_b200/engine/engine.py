@@ -47,6 +47,7 @@ class _Inflight:
     host: Optional[torch.Tensor]             # pinned copy under way (CUDA)
     event: Optional[object]
     row_of: dict                             # request id -> its row in `ids`
+    flag: Optional[torch.Tensor] = None      # pinned copy of the kernels' error flag, taken with the ids
 
 
 @dataclass
@@ -157,6 +158,13 @@ class Engine:
         self.scheduler.add(Request(request_id, prompt, params, max_tokens=max_tokens, eos_token_ids=eos, seed=seed))
         return request_id
 
+    def abort(self, request_id: Hashable) -> Optional[GenerationResult]:
+        """Stop a request now.  Its pages and slot go back to the pool at once, or, if the step in
+        flight still owes it a token, when that step's tokens are read (the next `step()` or `drain()`
+        then reports it with finish_reason "abort").  Returns the result if it is final already."""
+        r = self.scheduler.abort(request_id)
+        return None if r is None else self._result(r)
+
     def has_unfinished(self) -> bool:
         return self.scheduler.has_unfinished() or self._inflight is not None
 
@@ -189,18 +197,22 @@ class Engine:
             logits = self.runner.step(entries, relay=(relay, prev.ids) if relay else None)
             rows = [SamplingRow(e.request.params, e.request.seed, len(e.request.output), e.request.output)
                     for e in plan.entries if e.wants_logits]
-            ids = host = event = None
+            ids = host = event = flag = None
             if rows:
                 ids = self.sampler.sample(logits, rows)
                 if ids.is_cuda:
                     host = torch.empty(ids.shape, dtype=ids.dtype, pin_memory=True)
                     host.copy_(ids, non_blocking=True)          # the step's device-to-host read
+                    err = getattr(self.kernels, "error_flag", None)
+                    if err is not None:                         # a kernel whose bounded wait ran out set it
+                        flag = torch.empty(1, dtype=err.dtype, pin_memory=True)
+                        flag.copy_(err, non_blocking=True)
                     event = torch.cuda.Event()
                     event.record()
-                self.stats.d2h_bytes += 4 * len(rows)
+                self.stats.d2h_bytes += 4 * len(rows) + (4 if flag is not None else 0)
             self.scheduler.advance(plan)
             wanting = [e.request.request_id for e in plan.entries if e.wants_logits]
-            launched = _Inflight(plan, ids, host, event, {rid: i for i, rid in enumerate(wanting)})
+            launched = _Inflight(plan, ids, host, event, {rid: i for i, rid in enumerate(wanting)}, flag)
             self.stats.h2d_bytes += self.runner.last_ctx.meta_bytes
             self.stats.steps += 1
             self.stats.prompt_tokens += sum(e.count for e in plan.entries if e.count > 1 or not e.request.output)
@@ -223,8 +235,8 @@ class Engine:
             sampled = step.host.tolist()
         else:
             sampled = step.ids.tolist()
-        if self.stats.steps % 32 == 1 and hasattr(self.kernels, "check_errors"):
-            self.kernels.check_errors()                     # a kernel whose bounded wait ran out says so here
+        if step.flag is not None and int(step.flag[0]) != 0:
+            self.kernels.check_errors()                     # raises before the tokens of an invalid step are used
         return [self._result(r) for r in self.scheduler.resolve(step.plan, sampled)]
 
     def drain(self) -> List[GenerationResult]:
@@ -233,6 +245,8 @@ class Engine:
             return []
         out = self._finalize(self._inflight)
         self._inflight = None
+        if hasattr(self.kernels, "check_errors"):
+            self.kernels.check_errors()
         return out
 
     @staticmethod
@@ -257,4 +271,6 @@ class Engine:
             guard += 1
             if guard > 10_000_000:
                 raise RuntimeError("generation did not finish")
+        if hasattr(self.kernels, "check_errors"):
+            self.kernels.check_errors()                     # steps without sampled tokens carry no flag copy
         return [done[i] for i in ids]

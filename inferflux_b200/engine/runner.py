@@ -91,6 +91,9 @@ class ModelRunner:
                 raise StepError(f"request {e.request_id!r}: token ids {bad[:8]} are outside the vocabulary "
                                 f"of {self.vocab_size}")
             start = self.cache.length(e.request_id) if e.request_id in self.cache else 0
+            if e.start is not None and int(e.start) != start:
+                raise StepError(f"request {e.request_id!r}: the caller's tokens begin at {e.start}, the cache "
+                                f"holds {start}")
             if start + len(e.tokens) > self.max_seq_len:
                 raise StepError(f"request {e.request_id!r}: {start + len(e.tokens)} tokens exceed the longest "
                                 f"sequence of {self.max_seq_len}")
@@ -129,19 +132,28 @@ class ModelRunner:
         for rid in fresh:
             cache.add_request(rid)
         starts, slots = [], []
-        for e in entries:
-            start = cache.length(e.request_id)
-            cache.reserve(e.request_id, start + len(e.tokens))
-            starts.append(start)
-            slots.append(cache.slot(e.request_id))
-
-        ctx = StepContext.build(self.kernels, self.dtype, self.device, entries, starts, slots,
-                                cache.drain_table_updates(), relay[0] if relay else None,
-                                providers=getattr(self.model, "section_providers", ()))
-        for group, (index, page) in zip(cache.groups, ctx.table_updates):
-            self.kernels.scatter_i32(group.table, index, page)
-        ctx.relay_ids = relay[1] if relay else None
-        logits = self._forward(ctx, entries)
+        try:
+            for e in entries:
+                start = cache.length(e.request_id)
+                cache.reserve(e.request_id, start + len(e.tokens))
+                starts.append(start)
+                slots.append(cache.slot(e.request_id))
+            ctx = StepContext.build(self.kernels, self.dtype, self.device, entries, starts, slots,
+                                    cache.drain_table_updates(), relay[0] if relay else None,
+                                    providers=getattr(self.model, "section_providers", ()))
+            for group, (index, page) in zip(cache.groups, ctx.table_updates):
+                self.kernels.scatter_i32(group.table, index, page)
+            ctx.relay_ids = relay[1] if relay else None
+            logits = self._forward(ctx, entries)
+        except BaseException:
+            # nothing of this step counts: new requests leave again, the others give back what they took
+            for e in entries:
+                if e.request_id in fresh:
+                    if e.request_id in cache:
+                        cache.free(e.request_id)
+                elif e.request_id in cache:
+                    cache.release_uncommitted(e.request_id)
+            raise
         for e, start in zip(entries, starts):
             cache.commit(e.request_id, start + len(e.tokens))
         self.steps += 1

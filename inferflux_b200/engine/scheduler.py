@@ -100,7 +100,7 @@ class StepPlan:
         out = []
         for e in self.entries:
             toks = e.request.token_slice(e.start, e.count)
-            out.append(StepEntry(e.request.request_id, toks, [e.count - 1] if e.wants_logits else []))
+            out.append(StepEntry(e.request.request_id, toks, [e.count - 1] if e.wants_logits else [], start=e.start))
         return out
 
     @property
@@ -185,6 +185,37 @@ class Scheduler:
         if r in self.finishing:
             self.finishing.remove(r)
         self.finished.append(r)
+
+    def abort(self, request_id) -> Optional[Request]:
+        """End a request at once, whatever its state (the reference cancels between decode
+        iterations, runtime/execution/batch_executor.cpp:1406-1443, and releases slot and blocks
+        in scheduler/scheduler.cpp:2984-3001).  Returns the request if its pages and slot are free
+        now; None if a token of it is still pending in the step in flight (it is then freed, and
+        reported, when that step's tokens are read, like a request that met its end there) or if no
+        live request has that id."""
+        for r in self.waiting:
+            if r.request_id == request_id:
+                self.waiting.remove(r)
+                r.status, r.finish_reason = "finished", "abort"
+                self.finished.append(r)
+                return r
+        for r in self.running:
+            if r.request_id != request_id:
+                continue
+            if r.pending:                                   # the step in flight will bring a token for it
+                del r.output[len(r.output) - r.pending:]
+                r.pending = 0
+                r.discard = True
+                r.finish_reason = "abort"
+                r.status = "finishing"
+                self.running.remove(r)
+                self.finishing.append(r)
+                return None
+            # A prompt portion of it may be in flight too: its pages may still be given to the next
+            # step's requests, because that step runs after the one in flight, in stream order.
+            self._finish(r, "abort")
+            return r
+        return None
 
     # ---------------------------------------------------------------- schedule
     def _may_continue(self, r: Request) -> bool:

@@ -27,7 +27,7 @@ def load_model(model_dir, dtype="bfloat16", device="cuda"):
     dtype = parse_dtype(dtype)
     config = load_config(model_dir)
     model = Model(config.to_plan())
-    tensors = load_weights(model_dir, model.expected_tensors(), device=device)
+    tensors = load_weights(model_dir, model.expected_tensors(), device=device, run_dtype=dtype)
     model.load(tensors, dtype, device)
     return config, model
 

@@ -7,11 +7,19 @@ may be absent), and one `WeightError` lists everything that is missing, unexpect
 or wrongly shaped.
 
 Stored dtypes: 16-bit floats are kept as bfloat16, a tensor stored in 32-bit floats
-stays 32-bit, integer tables become int32.  Converting to the dtype a run computes
-in is the part's business when it takes its tensors.
+stays 32-bit, integer tables become int32.  A float32 run takes float16 tensors
+straight to float32, so that it does not compute with weights that lost three bits on
+the way through bfloat16.  Converting to the dtype a run computes in is otherwise the
+part's business when it takes its tensors.
+
+Buffers that older exports carry and no part uses (`IGNORED_SUFFIXES`) are skipped with
+a warning; so is the `lm_head.weight` of a model whose configuration ties the head to
+the embedding (the reference would use the tensor, runtime/backends/cuda/native/
+weight_map.cpp:33-37; here the configuration wins, and says so).
 """
 from __future__ import annotations
 
+import warnings
 from dataclasses import dataclass
 from typing import Dict, Optional, Tuple
 
@@ -49,19 +57,30 @@ class WeightError(ValueError):
         super().__init__("\n".join(lines))
 
 
-def stored_dtype(dt: torch.dtype) -> torch.dtype:
-    """The dtype a tensor of file dtype `dt` is kept in."""
+IGNORED_SUFFIXES = ("rotary_emb.inv_freq", "masked_bias", "attn.bias")     # buffers, not parameters
+
+
+def stored_dtype(dt: torch.dtype, run_dtype: Optional[torch.dtype] = None) -> torch.dtype:
+    """The dtype a tensor of file dtype `dt` is kept in (for a run that computes in `run_dtype`)."""
     if dt in (torch.float32, torch.float64):
         return torch.float32
     if dt.is_floating_point:
-        return torch.bfloat16
+        return torch.float32 if (dt == torch.float16 and run_dtype == torch.float32) else torch.bfloat16
     return torch.int32
 
 
 def check_tensors(found: Dict[str, Tuple[int, ...]], expected: Dict[str, TensorSpec], where: str = "") -> None:
     """Raise one WeightError if the shapes in `found` do not fit `expected`."""
     missing = [n for n, s in expected.items() if n not in found and not s.optional and not s.ignored]
-    unexpected = [n for n in found if n not in expected]
+    skipped = [n for n in found if n not in expected and n.endswith(IGNORED_SUFFIXES)]
+    if skipped:
+        warnings.warn(f"{where or 'weights'}: {len(skipped)} tensors that no part uses are skipped "
+                      f"({', '.join(sorted(skipped)[:3])}{', ...' if len(skipped) > 3 else ''})", stacklevel=3)
+    unused = [n for n, s in expected.items() if s.ignored and n in found]
+    if unused:
+        warnings.warn(f"{where or 'weights'}: {', '.join(sorted(unused))} is present but not used "
+                      f"(the configuration ties it to another tensor)", stacklevel=3)
+    unexpected = [n for n in found if n not in expected and not n.endswith(IGNORED_SUFFIXES)]
     wrong = [(n, tuple(found[n]), tuple(s.shape)) for n, s in expected.items()
              if n in found and not s.ignored and tuple(found[n]) != tuple(s.shape)]
     if missing or unexpected or wrong:
@@ -99,7 +118,8 @@ class _Staging:
             e.synchronize()
 
 
-def load_weights(model_dir, expected: Dict[str, TensorSpec], device="cpu") -> Dict[str, torch.Tensor]:
+def load_weights(model_dir, expected: Dict[str, TensorSpec], device="cpu",
+                 run_dtype: Optional[torch.dtype] = None) -> Dict[str, torch.Tensor]:
     """All tensors of a model folder that `expected` names, on `device`.  To a CUDA device the bytes go
     from the mapped file through pinned buffers; the dtype is converted there."""
     shards = open_model_shards(model_dir)
@@ -117,10 +137,10 @@ def load_weights(model_dir, expected: Dict[str, TensorSpec], device="cpu") -> Di
                 continue
             if staging is None:
                 t = owner[n].tensor(n)
-                out[n] = t.to(stored_dtype(t.dtype))
+                out[n] = t.to(stored_dtype(t.dtype, run_dtype))
             else:
                 t = owner[n].view(n)
-                out[n] = staging.to_device(t).to(stored_dtype(t.dtype))
+                out[n] = staging.to_device(t).to(stored_dtype(t.dtype, run_dtype))
                 del t
         if staging is not None:
             staging.finish()

@@ -223,3 +223,23 @@ def first_bad(got, want, tol):
         if bad.size:
             return rid, int(bad[0]), float(d[bad[0]])
     return None
+
+
+def plain_rows_layer_by_layer(cfg_raw, W, tokens, rows, dtype=torch.float64):
+    """Logits of the plain implementation at `rows` of one whole sequence, run layer by layer so
+    that only one layer's weights exist in `dtype` at a time (for models of many GB on the GPU).
+    `W` holds the weights as stored (bfloat16 or float32), on the device the work should run on."""
+    from plain import plain_qwen2 as P
+    dev = W["model.embed_tokens.weight"].device
+    toks = torch.as_tensor(tokens, dtype=torch.long, device=dev)
+    positions = torch.arange(toks.numel())
+    x = P.embedding(W["model.embed_tokens.weight"], toks).to(dtype)
+    for layer in range(cfg_raw["num_hidden_layers"]):
+        prefix = f"model.layers.{layer}."
+        Wl = {k: v.to(dtype) for k, v in W.items() if k.startswith(prefix)}
+        x = P.decoder_layer(x, Wl, cfg_raw, layer, positions)
+        del Wl
+    tied = cfg_raw.get("tie_word_embeddings", False) or "lm_head.weight" not in W
+    table = "model.embed_tokens.weight" if tied else "lm_head.weight"
+    head = {"model.norm.weight": W["model.norm.weight"].to(dtype), table: W[table].to(dtype)}
+    return P.lm_head(x[torch.as_tensor(rows, device=dev)], head, cfg_raw)

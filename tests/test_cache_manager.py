@@ -141,3 +141,28 @@ def test_random_orders_keep_the_books(seed):
     m.check()
     assert m.free_pages() == [24, 24] and m.num_free_slots == 5
     assert m.groups[0].alloc.allocations > 24, "pages were never used again"
+
+
+def test_a_failed_step_gives_back_what_it_reserved():
+    from inferflux_b200.cache import CacheManager
+    from inferflux_b200.parts import KVCacheSpec
+    import torch
+    cm = CacheManager([(KVCacheSpec(1, 8, None), None), (KVCacheSpec(1, 8, 6), None)], page_size=4, num_pages=10,
+                      max_seqs=2, max_seq_len=64, dtype=torch.float32, device="cpu")
+    cm.add_request("a")
+    cm.reserve("a", 9)
+    cm.commit("a", 9)
+    cm.drain_table_updates()
+    free = cm.free_pages()
+    held = cm.pages_of("a", 0)
+    cm.reserve("a", 22)                                    # the step takes pages ...
+    assert cm.free_pages() != free
+    cm.release_uncommitted("a")                            # ... and fails before commit
+    assert cm.free_pages() == free and cm.pages_of("a", 0) == held and cm.length("a") == 9
+    assert all(not ups for ups in cm.drain_table_updates())
+    cm.check()
+    cm.reserve("a", 13)                                    # and goes on as if nothing had happened
+    cm.commit("a", 13)
+    cm.check()
+    cm.free("a")
+    assert cm.free_pages() == [10, 10]

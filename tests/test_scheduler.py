@@ -195,3 +195,47 @@ def test_validation():
         e.add([], max_tokens=3)
     with pytest.raises(ValueError):
         e.sched.add(Request("x", [1], SamplingParams(top_p=0.0)))
+
+
+def test_abort_frees_pages_now_or_when_the_step_in_flight_is_read():
+    """A waiting request leaves the queue; a running one gives its pages back at once and the pool
+    serves the others with them; one that is owed a token by a step in flight is freed when that
+    step's tokens are read, and its token is dropped."""
+    eng = FakeEngine(num_pages=12, page=4, max_seqs=3, max_batch_size=3, chunked_prefill_tokens=16)
+    a = eng.add(list(range(1, 17)), max_tokens=20)          # 16 tokens = 4 pages, grows to 9
+    b = eng.add(list(range(20, 36)), max_tokens=20)
+    c = eng.add(list(range(40, 56)), max_tokens=20)
+    w = eng.add(list(range(60, 70)), max_tokens=4)          # waits: three slots
+    eng.step()
+    assert {r.request_id for r in eng.sched.running} == {a, b, c}
+    # waiting -> gone
+    r = eng.sched.abort(w)
+    assert r is not None and r.finish_reason == "abort" and not eng.sched.waiting
+    # running, nothing pending -> freed at once
+    free_before = eng.cache.free_pages()[0]
+    r = eng.sched.abort(b)
+    assert r is not None and r.finish_reason == "abort" and b not in eng.cache
+    assert eng.cache.free_pages()[0] == free_before + 4     # the 16 prompt tokens it had stored
+    eng.cache.check()
+    # pending (a step in flight): advance without resolve, abort, then resolve
+    plan = eng.sched.schedule()
+    for e in plan.entries:
+        eng.cache.reserve(e.request.request_id, e.start + e.count)
+        eng.cache.commit(e.request.request_id, e.start + e.count)
+    eng.sched.advance(plan)
+    assert eng.sched.abort(a) is None                        # its token is still coming
+    assert a in eng.cache and eng.sched.has_unfinished()
+    nxt = eng.sched.schedule(inflight=True)                  # the next step goes on without it
+    assert a not in {e.request.request_id for e in nxt.entries}
+    done = eng.sched.resolve(plan, [7] * sum(e.wants_logits for e in plan.entries))
+    assert [r.request_id for r in done] == [a] and done[0].finish_reason == "abort" and a not in eng.cache
+    assert -1 not in done[0].output
+    eng.cache.check()
+    assert eng.sched.abort("nobody") is None
+    # the rest finishes with the pages that came back
+    for e in nxt.entries:
+        eng.cache.reserve(e.request.request_id, e.start + e.count)
+        eng.cache.commit(e.request.request_id, e.start + e.count)
+    eng.sched.update(nxt, [3] * sum(e.wants_logits for e in nxt.entries))
+    eng.seen.clear()
+    eng.cache.check()

@@ -97,8 +97,28 @@ def test_biases_are_optional_and_tied_head_is_not_required(tmp_path):
     assert model.lm_head.weight is model.embedding.table
     # a tied model whose file also carries lm_head.weight: the configuration decides, the tensor is ignored
     rewrite(d / "model.safetensors", lambda t: t.update({"lm_head.weight": torch.zeros(100, 32)}))
-    _c, model = load_model(d, dtype="float32", device="cpu")
+    with pytest.warns(UserWarning, match="lm_head.weight is present but not used"):
+        _c, model = load_model(d, dtype="float32", device="cpu")
     assert model.lm_head.weight is model.embedding.table
+    # buffers of older exports that no part uses are skipped with a warning, not an error
+    rewrite(d / "model.safetensors", lambda t: (t.pop("lm_head.weight"),
+                                                t.update({"model.layers.0.self_attn.rotary_emb.inv_freq": torch.ones(8)})))
+    with pytest.warns(UserWarning, match="skipped"):
+        load_model(d, dtype="float32", device="cpu")
+
+
+def test_a_float16_file_reaches_a_32_bit_run_without_passing_through_bfloat16(tmp_path):
+    """float16 has three more bits than bfloat16: a float32 run computes with the file's own values."""
+    d = write_random_model(CFG, tmp_path / "m", seed=4, dtype=torch.float32)
+    rewrite(d / "model.safetensors", lambda t: t.update({n: v.to(torch.float16) for n, v in t.items()}))
+    with SafetensorsFile(d / "model.safetensors") as f:
+        halves = {n: f.tensor(n) for n in f.names()}
+    assert all(v.dtype == torch.float16 for v in halves.values())
+    _c, model = load_model(d, dtype="float32", device="cpu")
+    assert torch.equal(model.layers[0].ffn.w_down, halves["model.layers.0.mlp.down_proj.weight"].float())
+    assert not torch.equal(model.layers[0].ffn.w_down, halves["model.layers.0.mlp.down_proj.weight"].to(torch.bfloat16).float())
+    _c, model16 = load_model(d, dtype="bfloat16", device="cpu")
+    assert model16.layers[0].ffn.w_down.dtype == torch.bfloat16
 
 
 def test_stored_dtypes(tmp_path):

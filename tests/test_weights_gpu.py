@@ -54,3 +54,24 @@ def test_the_same_seed_gives_the_same_bits_on_the_host_and_on_the_device(tmp_pat
         dev = counter_normal((3, 1_400_001), seed, "x.weight", 0.0, 0.02, torch.float32, "cuda:0")
         assert torch.equal(host, dev.cpu())
     assert abs(float(host.std()) - 0.02) < 2e-4 and abs(float(host.mean())) < 1e-4
+
+
+def test_a_float16_file_in_a_32_bit_run_matches_the_plain_implementation(tmp_path, cuda_kernels):
+    """The 32-bit path computes with the float16 values of the file, not with their bfloat16 roundings."""
+    import helpers
+    from inferflux_b200.engine import ModelRunner, StepEntry
+    from inferflux_b200.models import load_model
+    from inferflux_b200.weights import SafetensorsFile, write_safetensors
+    from plain import plain_qwen2
+    cfg, _page = helpers.tiny_configs()["B"]
+    d = helpers.write_tiny_model(cfg, tmp_path / "m", seed=21, dtype=torch.float32)
+    with SafetensorsFile(d / "model.safetensors") as f:
+        tensors = {n: f.tensor(n).to(torch.float16) for n in f.names()}
+    write_safetensors(d / "model.safetensors", tensors, metadata={"format": "pt"})
+    toks = helpers.random_tokens(cfg.vocab_size, 45, 5)
+    raw, W = plain_qwen2.load_model_dir(d)
+    want = plain_qwen2.forward(raw, W, toks, dtype=torch.float64)
+    _c, model = load_model(d, dtype="float32", device="cuda:0")
+    runner = ModelRunner(model, cuda_kernels, page_size=8, num_pages=8, max_seqs=2)
+    got = runner.step([StepEntry("r", toks, list(range(len(toks))))]).double().cpu()
+    assert float((got - want).abs().max()) < 1e-4
