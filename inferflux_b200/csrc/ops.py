@@ -418,6 +418,10 @@ class CudaKernels:
         win = 0 if window is None else int(window)
         common = (cache.page_size, table.shape[1], kv.shape[0], win, ctypes.c_float(scale))
         tiled = q.dtype == torch.bfloat16 and bool(self.lib.ifx_attention_mma_supports(d))
+        if "attn.prefill_tiles" not in ctx.extra:          # a step context built without the mixer as a provider
+            for name, vals in self.attention_sections(ctx).items():
+                ctx.extra[name] = torch.tensor(vals, dtype=torch.int32, device=q.device)
+                ctx.extra_len[name] = len(vals)
         tiles, num_tiles = ctx.extra["attn.prefill_tiles"], ctx.extra_len["attn.prefill_tiles"] // 4
         decode_rows, decode_meta = ctx.extra["attn.decode_rows"], ctx.extra["attn.decode_meta"]
         if not tiled:

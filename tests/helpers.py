@@ -201,14 +201,15 @@ def run_trace_cli(model_dir, dtype, steps, out_dir, max_tokens, vocab, page_size
     return outputs
 
 
-def plain_logits(model_dir, requests, weights_as=None):
+def plain_logits(model_dir, requests, weights_as=None, dtype=torch.float64):
     """request id -> float64 logits [len, vocab] of the plain implementation.
-    `weights_as` rounds the stored weights first (what a bfloat16 run computes with)."""
+    `weights_as` rounds the stored weights first (what a bfloat16 run computes with);
+    `dtype` is the arithmetic (bfloat16: the yardstick of what rounding does)."""
     from plain import plain_qwen2
     cfg, W = plain_qwen2.load_model_dir(model_dir)
     if weights_as is not None:
         W = {k: v.to(weights_as) for k, v in W.items()}
-    return {rid: plain_qwen2.forward(cfg, W, toks, dtype=torch.float64).numpy() for rid, toks in requests.items()}
+    return {rid: plain_qwen2.forward(cfg, W, toks, dtype=dtype).double().numpy() for rid, toks in requests.items()}
 
 
 def max_abs_diff(got, want):
@@ -243,3 +244,33 @@ def plain_rows_layer_by_layer(cfg_raw, W, tokens, rows, dtype=torch.float64):
     table = "model.embed_tokens.weight" if tied else "lm_head.weight"
     head = {"model.norm.weight": W["model.norm.weight"].to(dtype), table: W[table].to(dtype)}
     return P.lm_head(x[torch.as_tensor(rows, device=dev)], head, cfg_raw)
+
+
+def bf16_check(name, got, want, yard, rows=None):
+    """bfloat16 results `got` against the exact ones `want`, row by row [rows, vocab].  The bound is not a
+    chosen number: `yard` is the plain implementation run in bfloat16 arithmetic on the same rounded
+    weights, and the engine, which keeps its sums and its residual stream in float32, has to be at least
+    as close to `want` as that, in the worst row and on average, and to agree on the best token as often."""
+    err = np.abs(got - want).max(axis=1)
+    bound = np.abs(yard - want).max(axis=1)
+    where = int(err.argmax()) if rows is None else rows[int(err.argmax())]
+    assert float(err.max()) <= float(bound.max()), \
+        f"{name}: row {where} is off by {float(err.max()):.4f}; plain bfloat16 arithmetic is off by at most {float(bound.max()):.4f}"
+    assert float(err.mean()) <= float(bound.mean()), f"{name}: mean error {float(err.mean()):.4f} against {float(bound.mean()):.4f}"
+    agree = float(np.mean(got.argmax(-1) == want.argmax(-1)))
+    assert agree >= float(np.mean(yard.argmax(-1) == want.argmax(-1))) - 0.05, f"{name}: best token agrees at {agree:.2f}"
+    return float(err.max()), float(bound.max())
+
+
+def chosen_tokens_follow(raw, W16, prompt, out, name=""):
+    """Every token of `out` (greedy) is the best, within rounding, under the plain logits of the sequence
+    it continues: the gap to the best logit is at most twice what bfloat16 arithmetic moves that row."""
+    from plain import plain_qwen2
+    seq = list(prompt) + list(out)
+    exact = plain_qwen2.forward(raw, W16, seq, dtype=torch.float64)
+    rough = plain_qwen2.forward(raw, W16, seq, dtype=torch.bfloat16).double()
+    for i, tok in enumerate(out):
+        row = len(prompt) - 1 + i
+        gap = float(exact[row].max() - exact[row, tok])
+        slack = 2.0 * float((rough[row] - exact[row]).abs().max())
+        assert gap <= slack, f"{name} token {i}: {gap:.4f} below the best logit, rounding allows {slack:.4f}"

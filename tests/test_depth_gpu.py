@@ -68,16 +68,7 @@ def test_7b_sizes_four_layers_in_32_bit(cuda_kernels):
     assert not runner.cache.live_requests()
 
 
-def bf16_check(name, got, want, yard, rows):
-    """`got` against the float64 result `want`, with the plain implementation in bfloat16 (`yard`) as the bound."""
-    err = np.abs(got - want).max(axis=1)
-    bound = np.abs(yard - want).max(axis=1)
-    assert float(err.max()) <= float(bound.max()), \
-        f"{name}: position {rows[int(err.argmax())]} is off by {float(err.max()):.4f}; plain bfloat16 arithmetic is off by at most {float(bound.max()):.4f}"
-    assert float(err.mean()) <= float(bound.mean()), f"{name}: mean error {float(err.mean()):.4f} against {float(bound.mean()):.4f}"
-    agree = float(np.mean(got.argmax(-1) == want.argmax(-1)))
-    assert agree >= float(np.mean(yard.argmax(-1) == want.argmax(-1))) - 0.05, f"{name}: best token agrees at {agree:.2f}"
-    return float(err.max()), float(bound.max())
+bf16_check = helpers.bf16_check
 
 
 @pytest.mark.parametrize("shape,layers", [("7b", 28), ("7b", 4), ("1.5b", 28), ("32b", 4)])

@@ -162,7 +162,8 @@ def test_command_line_streams_the_tokens_it_reports(model_dirs):
 def test_many_requests_with_every_kind_of_sampling_twice(model_dirs, tiny_configs):
     """Sixty requests of random lengths and sampling settings (greedy, temperature, top-k, top-p, min-p,
     penalties, stop tokens) through a pool so small that requests are preempted, with overlapped steps:
-    every request finishes, every page comes back, and a second run draws the same tokens."""
+    every request finishes, every page comes back, a second run draws the same tokens, and the greedy
+    requests' tokens are the best ones under the plain implementation's logits."""
     import random
     from inferflux_b200 import Engine, SamplingParams
     cfg, page = tiny_configs["E"]
@@ -199,9 +200,62 @@ def test_many_requests_with_every_kind_of_sampling_twice(model_dirs, tiny_config
     first, preemptions = run()
     second, _ = run()
     assert first == second
+    # against the oracle: what the greedy requests chose is the best token of the plain logits of their
+    # own sequence, within bfloat16 rounding (a wrong page or a stale key after a preemption would show)
+    raw, W = plain_qwen2.load_model_dir(d)
+    W16 = {k: v.to(torch.bfloat16) for k, v in W.items()}
+    checked = 0
+    for i, ((toks, _reason), (prompt, _sp, _m, _eos)) in enumerate(zip(first, jobs)):
+        if i % 6 == 0:
+            helpers.chosen_tokens_follow(raw, W16, prompt, toks, f"request {i}")
+            checked += 1
+    assert checked == 10
     assert preemptions > 0, "the pool was large enough that nothing was preempted"
     for (toks, reason), (_p, _sp, m, eos) in zip(first, jobs):
         assert 1 <= len(toks) <= m and all(0 <= t < cfg.vocab_size for t in toks)
         assert reason in ("length", "stop")
         if reason == "stop":
             assert toks[-1] == eos
+
+
+def test_abort_with_a_step_in_flight_frees_pages_that_the_waiting_request_then_uses(model_dirs, tiny_configs):
+    """Three requests fill the pool and a fourth waits.  One of the three is aborted while a step that
+    owes it a token is in flight (steps overlap): it is reported with `abort`, its pages come back, the
+    waiting request runs on them, and everyone else's tokens are what they are without the episode."""
+    from inferflux_b200 import Engine, SamplingParams
+    cfg, page = tiny_configs["B"]
+    d, _ = model_dirs["B"]
+    prompts = [helpers.random_tokens(cfg.vocab_size, n, 900 + i) for i, n in enumerate([40, 44, 36, 30])]
+    raw, W = plain_qwen2.load_model_dir(d)
+    want = [plain_qwen2.greedy_generate(raw, W, p, 14) for p in prompts]
+    pages = 3 * (-(-(44 + 16) // page))                      # room for three, not for four
+    eng = Engine(d, dtype="float32", kv_page_size=page, kv_num_pages=pages, kv_max_batch=3, kv_max_seq=96,
+                 chunked_prefill_tokens=64, max_batch_tokens=256, overlap_steps=True)
+    ids = [eng.add_request(p, SamplingParams(temperature=0.0), max_tokens=14) for p in prompts]
+    done = {}
+    for _ in range(4):
+        for r in eng.step():
+            done[r.request_id] = r
+    assert eng._inflight is not None and ids[3] not in eng.runner.cache
+    victim = ids[1]
+    assert eng.abort(victim) is None                         # the step in flight still owes it a token
+    assert eng.abort("no-such-request") is None
+    while eng.has_unfinished():
+        for r in eng.step():
+            done[r.request_id] = r
+    assert done[victim].finish_reason == "abort" and -1 not in done[victim].token_ids
+    assert done[victim].token_ids == want[1][:len(done[victim].token_ids)] and len(done[victim].token_ids) < 14
+    for i in (0, 2, 3):
+        assert done[ids[i]].token_ids == want[i] and done[ids[i]].finish_reason == "length"
+    assert not eng.runner.cache.live_requests()
+    g0 = eng.runner.cache.stats()["groups"][0]
+    assert g0["free"] == g0["pages"]
+    eng.runner.cache.check()
+    # a request that only waits is gone at once, one that runs with nothing pending too
+    eng2 = Engine(d, dtype="float32", kv_page_size=page, kv_num_pages=pages, kv_max_batch=3, kv_max_seq=96, overlap_steps=False)
+    a, b = (eng2.add_request(p, SamplingParams(temperature=0.0), max_tokens=6) for p in prompts[:2])
+    assert eng2.abort(b).finish_reason == "abort"
+    eng2.step()
+    res = eng2.abort(a)
+    assert res.finish_reason == "abort" and len(res.token_ids) == 1 and not eng2.has_unfinished()
+    assert not eng2.runner.cache.live_requests()

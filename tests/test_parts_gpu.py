@@ -104,8 +104,9 @@ def test_attention_part_alone(cuda_kernels, dtype, tol):
         outs, pos = [], 0
         for n in cuts:
             cache.reserve("r", pos + n)
+            # the mixer's own step arrays travel with the step's metadata (or, for the 17, are made when first used)
             ctx = StepContext.build(cuda_kernels, dtype, DEV, [StepEntry("r", [0] * n, [])], [pos], [cache.slot("r")],
-                                    cache.drain_table_updates())
+                                    cache.drain_table_updates(), providers=[mixer] if n != 17 else [])
             for g, (idx, page) in zip(cache.groups, ctx.table_updates):
                 cuda_kernels.scatter_i32(g.table, idx, page)
             outs.append(cuda_kernels.materialize(mixer.forward(h[pos:pos + n].to(DEV).contiguous(), ctx,

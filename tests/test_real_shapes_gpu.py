@@ -116,3 +116,39 @@ def test_long_context_at_a_real_shape(cuda_kernels):
         assert float(d.max()) < 0.03 * scale, f"{name}: position {wanted[int(d.argmax())]} differs by {float(d.max())} (scale {scale})"
     cuda_kernels.check_errors()
     assert not runner.cache.live_requests()
+
+
+def test_mixed_steps_at_the_7b_layer_sizes_with_pages_used_again(cuda_kernels):
+    """Head size 128, pages of 16, seven query heads a group: six requests, up to four live, portions of
+    some beside decoded tokens of others, through a pool of 28 pages, so that a finished request's pages
+    serve the next one.  Queries and keys are scaled up so that attention is peaked and a wrong or stale
+    page moves the logits; every row against the plain implementation, in bfloat16, bounded by what
+    plain bfloat16 arithmetic does to the same rows."""
+    from inferflux_b200.config import Qwen2Config
+    from inferflux_b200.engine import ModelRunner
+    from inferflux_b200.models import Model
+    from inferflux_b200.weights import random_tensors
+    from plain import plain_qwen2
+    cfg = Qwen2Config(num_hidden_layers=1, max_position_embeddings=512, **SHAPES["7b"])
+    model = Model(cfg.to_plan())
+    W = random_tensors(model.expected_tensors(), 12, dtype=torch.bfloat16, device="cuda:0", norm_jitter=0.2)
+    for n in W:
+        if ".q_proj." in n or ".k_proj." in n:
+            W[n] = (W[n].float() * 3.0).to(torch.bfloat16)
+    model.load(dict(W), torch.bfloat16, "cuda:0")
+    pages = 28
+    runner = ModelRunner(model, cuda_kernels, page_size=16, num_pages=pages, max_seqs=4, cuda_graphs=True)
+    reqs = {f"m{i}": helpers.random_tokens(cfg.vocab_size, n, 800 + i) for i, n in enumerate([100, 70, 130, 40, 90, 60])}
+    raw = cfg.to_dict()
+    want = {r: plain_qwen2.forward(raw, W, t, dtype=torch.float64).cpu().numpy() for r, t in reqs.items()}
+    yard = {r: plain_qwen2.forward(raw, W, t, dtype=torch.bfloat16).float().cpu().numpy() for r, t in reqs.items()}
+    del W
+    torch.cuda.empty_cache()
+    steps = helpers.trace_mixed(reqs, pages * 16)
+    assert max(len(s["entries"]) for s in steps) >= 3
+    got = helpers.collect(steps, helpers.run_steps_in_process(runner, steps), cfg.vocab_size)
+    g0 = runner.cache.stats()["groups"][0]
+    assert g0["allocations"] > pages and g0["free"] == pages, "no page was used a second time"
+    for rid in reqs:
+        helpers.bf16_check(f"mixed at 7B sizes, {rid}", got[rid], want[rid], yard[rid])
+    cuda_kernels.check_errors()

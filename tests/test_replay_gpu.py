@@ -30,7 +30,7 @@ def make_runner(model_dir, page, dtype, cuda_kernels, max_tokens=MAX_TOKENS):
     return ModelRunner(model, cuda_kernels, page_size=page, num_pages=max_tokens // page, max_seqs=8)
 
 
-def check(got, want, dtype, what):
+def check(got, want, dtype, what, yard=None):
     if dtype == "float32":
         bad = helpers.first_bad(got, want, 1e-4)
         assert bad is None, f"{what}: first wrong row (request, position, diff) = {bad}"
@@ -42,6 +42,9 @@ def check(got, want, dtype, what):
         assert bad is None, f"{what}: first wrong row (request, position, diff) = {bad}, scale {scale}"
         mean = np.mean([np.abs(got[r] - want[r]).mean() for r in want])
         assert mean < 0.006 * scale, f"{what}: mean error {mean} at scale {scale}"
+        if yard is not None:         # and no further from the exact logits than plain bfloat16 arithmetic is
+            for rid in want:
+                helpers.bf16_check(f"{what} {rid}", got[rid], want[rid], yard[rid])
 
 
 @pytest.fixture(scope="module")
@@ -50,7 +53,8 @@ def oracle(model_dirs, tiny_configs):
     for name, (d, _page) in model_dirs.items():
         reqs = requests_for(tiny_configs[name][0])
         out[name] = {"float32": helpers.plain_logits(d, reqs),
-                     "bfloat16": helpers.plain_logits(d, reqs, weights_as=torch.bfloat16)}
+                     "bfloat16": helpers.plain_logits(d, reqs, weights_as=torch.bfloat16),
+                     "yard": helpers.plain_logits(d, reqs, weights_as=torch.bfloat16, dtype=torch.bfloat16)}
     return out
 
 
@@ -66,7 +70,7 @@ def test_step_function_cuttings(name, dtype, cutting, model_dirs, tiny_configs, 
     runner = make_runner(d, page, dtype, cuda_kernels)
     outputs = helpers.run_steps_in_process(runner, steps)
     got = helpers.collect(steps, outputs, cfg.vocab_size)
-    check(got, oracle[name][dtype], dtype, f"{name}/{dtype}/{cutting}")
+    check(got, oracle[name][dtype], dtype, f"{name}/{dtype}/{cutting}", oracle[name]["yard"])
     assert not runner.cache.live_requests()
     if cutting == "mixed":
         g0 = runner.cache.stats()["groups"][0]
@@ -165,7 +169,39 @@ def test_decode_steps_replayed_from_a_cuda_graph(dtype, model_dirs, tiny_configs
                          cuda_graphs=True)
     got = helpers.collect(steps, helpers.run_steps_in_process(runner, steps), cfg.vocab_size)
     assert runner.graph_replays >= 30
-    check(got, {k: oracle[name][dtype][k] for k in reqs}, dtype, f"graph replay {dtype}")
+    check(got, {k: oracle[name][dtype][k] for k in reqs}, dtype, f"graph replay {dtype}", oracle[name]["yard"])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_nine_live_requests_of_different_lengths_decode_from_a_cuda_graph(dtype, model_dirs, tiny_configs, cuda_kernels):
+    """Nine requests of different lengths (some past the window, some inside their first page) decode
+    together for twenty steps: from the second step on every step is a replay of one captured graph over
+    metadata at fixed addresses.  Every logits row against the plain implementation."""
+    from inferflux_b200.engine import ModelRunner, StepEntry
+    from inferflux_b200.models import load_model
+    name = "E"
+    cfg, page = tiny_configs[name]
+    d, _ = model_dirs[name]
+    lens = [3, 17, 64, 150, 151, 200, 33, 96, 129]
+    tail = 20
+    reqs = {f"g{i}": helpers.random_tokens(cfg.vocab_size, n + tail, 500 + i) for i, n in enumerate(lens)}
+    want = helpers.plain_logits(d, reqs, weights_as=torch.bfloat16 if dtype == "bfloat16" else None)
+    yard = helpers.plain_logits(d, reqs, weights_as=torch.bfloat16, dtype=torch.bfloat16) if dtype == "bfloat16" else None
+    _c, model = load_model(d, dtype=dtype, device="cuda:0")
+    runner = ModelRunner(model, cuda_kernels, page_size=page, num_pages=sum(-(-(n + tail) // page) for n in lens),
+                         max_seqs=9, cuda_graphs=True)
+    got = {rid: [] for rid in reqs}
+    for (rid, toks), n in zip(reqs.items(), lens):          # prompts one by one, each whole
+        out = runner.step([StepEntry(rid, toks[:n], list(range(n)))])
+        got[rid] += list(out.float().cpu().numpy())
+    before = runner.graph_replays
+    for i in range(tail):
+        out = runner.step([StepEntry(rid, [toks[n + i]], [0]) for (rid, toks), n in zip(reqs.items(), lens)])
+        for k, rid in enumerate(reqs):
+            got[rid].append(out[k].float().cpu().numpy())
+    assert runner.graph_replays - before >= tail - 1
+    check({rid: np.stack(v) for rid, v in got.items()}, want, dtype, f"nine live {dtype}", yard)
+    cuda_kernels.check_errors()
 
 
 @pytest.mark.parametrize("name,dtype", [("E", "bfloat16"), ("E", "float32"), ("C", "bfloat16")])
