@@ -8,7 +8,7 @@ written for B200 (sm_100a).
 __version__ = "0.1.0"
 
 from .config import Qwen2Config, load_config
-from .engine import Engine, GenerationResult
+from .engine import Engine, GenerationResult, ModelLoadSpec
 from .sampling import SamplingParams
 
-__all__ = ["Engine", "GenerationResult", "SamplingParams", "Qwen2Config", "load_config"]
+__all__ = ["Engine", "GenerationResult", "ModelLoadSpec", "SamplingParams", "Qwen2Config", "load_config"]

@@ -108,6 +108,13 @@ class Engine:
         self._next_id = 0
         self.stats = EngineStats()
 
+    @classmethod
+    def from_spec(cls, spec, **overrides) -> "Engine":
+        """An engine for a `ModelLoadSpec` (what the command line and the replay program build)."""
+        kw = spec.checked().engine_kwargs()
+        kw.update(overrides)
+        return cls(spec.path, **kw)
+
     # ------------------------------------------------------------------ sizing
     def bytes_per_token(self) -> int:
         """Cache bytes one token takes over all caches (2 . layers . kv_heads . head_dim . itemsize

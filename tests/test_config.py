@@ -106,3 +106,36 @@ def test_a_head_size_the_kernels_do_not_take_is_refused_when_the_config_is_read(
             config_from_dict(dict(raw, head_dim=head_dim))
     for head_dim in (8, 24, 128, 256):
         assert config_from_dict(dict(raw, head_dim=head_dim)).head_dim == head_dim
+
+
+def test_model_load_spec_validates_and_feeds_the_engine(tmp_path):
+    from inferflux_b200.engine import ModelLoadSpec
+    ok = ModelLoadSpec(path="m", dtype="float32", context_size=512, max_parallel_sequences=4, kv_num_pages=64)
+    assert ok.validate() == "" and ok.name == "m"
+    kw = ok.engine_kwargs()
+    assert kw["kv_max_batch"] == 4 and kw["kv_max_seq"] == 512 and kw["dtype"] == "float32" and kw["kv_num_pages"] == 64
+    for change, word in ((dict(path=""), "path"), (dict(format="gguf"), "format"), (dict(dtype="int8"), "dtype"),
+                         (dict(device="rocm:0"), "device"), (dict(context_size=0), "context_size"),
+                         (dict(max_parallel_sequences=300), "max_parallel_sequences"),
+                         (dict(kv_cache_type="q8_0"), "kv_cache_type"), (dict(kv_page_size=0), "kv_page_size"),
+                         (dict(kv_budget_ratio=0.0), "kv_budget_ratio"), (dict(max_batch_tokens=0), "max_batch_tokens")):
+        import dataclasses
+        bad = dataclasses.replace(ok, **change)
+        assert word in bad.validate()
+        with pytest.raises(ValueError, match="model load spec"):
+            bad.checked()
+
+
+def test_inferctl_info_describes_a_model_folder(tmp_path, capsys):
+    import json
+    import torch
+    from inferflux_b200.cli.main import main
+    from inferflux_b200.config import Qwen2Config
+    from inferflux_b200.weights import write_random_model
+    cfg = Qwen2Config(hidden_size=64, num_hidden_layers=3, num_attention_heads=4, num_key_value_heads=2, head_dim=16,
+                      intermediate_size=96, vocab_size=128)
+    write_random_model(cfg, tmp_path, seed=1, dtype=torch.bfloat16)
+    assert main(["info", "--model", str(tmp_path)]) == 0
+    out = json.loads(capsys.readouterr().out)
+    assert out["model"]["architecture"] == "Qwen2ForCausalLM" and out["model"]["kv_bytes_per_token_bf16"] == 2 * 3 * 2 * 16 * 2
+    assert "attention" in out["engine"]["parts"]["mixer"]
