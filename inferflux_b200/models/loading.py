@@ -4,7 +4,7 @@ from __future__ import annotations
 import torch
 
 from ..config import load_config
-from ..weights import load_weights, random_tensors
+from ..weights import WeightSource, random_tensors
 from .model import Model
 
 _DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32}
@@ -27,8 +27,8 @@ def load_model(model_dir, dtype="bfloat16", device="cuda"):
     dtype = parse_dtype(dtype)
     config = load_config(model_dir)
     model = Model(config.to_plan())
-    tensors = load_weights(model_dir, model.expected_tensors(), device=device, run_dtype=dtype)
-    model.load(tensors, dtype, device)
+    with WeightSource(model_dir, model.expected_tensors(), device=device, run_dtype=dtype) as source:
+        model.load(source.take, dtype, device)              # part by part
     return config, model
 
 
@@ -37,14 +37,9 @@ def random_model(config, seed=0, dtype="bfloat16", device="cuda", std=0.02, norm
     dtype = parse_dtype(dtype)
     model = Model(config.to_plan())
     store = torch.float32 if dtype == torch.float32 else torch.bfloat16
-    # Part by part, so that at most one part's unpacked tensors exist beside the model.
-    model.dtype, model.device = dtype, torch.device(device)
-    for prefix, part in model.named_parts():
-        own_specs = {prefix + n: s for n, s in part.param_specs().items()}
-        made = random_tensors(own_specs, seed, dtype=store, device=device, std=std, norm_jitter=norm_jitter)
-        own = {n[len(prefix):]: t for n, t in made.items()}
-        if part is model.lm_head:
-            part.load(own, dtype, device, tied_table=model.embedding.table)
-        else:
-            part.load(own, dtype, device)
-    return model
+    expected = model.expected_tensors()
+
+    def make(names):                                        # part by part, as a folder is loaded
+        return random_tensors({n: expected[n] for n in names}, seed, dtype=store, device=device, std=std,
+                              norm_jitter=norm_jitter)
+    return model.load(make, dtype, device)

@@ -69,15 +69,21 @@ class Model:
                 out[prefix + name] = spec
         return out
 
-    def load(self, tensors: Dict[str, torch.Tensor], dtype: torch.dtype, device) -> "Model":
-        """Hand every part its tensors (already checked against expected_tensors)."""
+    def load(self, tensors, dtype: torch.dtype, device) -> "Model":
+        """Hand every part its tensors (already checked against expected_tensors).  `tensors` is a
+        dict name -> tensor, or a function that brings the tensors of the names it is given (a
+        part at a time, so that only one part's unpacked tensors exist beside the model)."""
         self.dtype, self.device = dtype, torch.device(device)
         for prefix, part in self.named_parts():
-            own = {n: tensors[prefix + n] for n in part.param_specs() if (prefix + n) in tensors}
+            names = [prefix + n for n in part.param_specs()]
+            got = tensors(names) if callable(tensors) else tensors
+            own = {n[len(prefix):]: got[n] for n in names if n in got}
+            del got
             if part is self.lm_head:
                 part.load(own, dtype, device, tied_table=self.embedding.table)
             else:
                 part.load(own, dtype, device)
+            del own
         return self
 
     # ------------------------------------------------------------------ cache needs

@@ -18,7 +18,7 @@ import math
 import torch
 
 from ..weights.loader import TensorSpec
-from .base import KVCacheSpec, Mixer, build_part, register_part
+from .base import KVCacheSpec, Mixer, WeightBuffers, build_part, register_part
 
 
 @register_part("mixer", "attention")
@@ -74,19 +74,25 @@ class Attention(Mixer):
         return specs
 
     def load(self, tensors, dtype, device):
-        mats = [tensors[n + "_proj.weight"].to(device=device, dtype=dtype) for n in ("q", "k", "v")]
-        self.w_qkv = torch.cat(mats, dim=0).contiguous()
-        self.w_o = tensors["o_proj.weight"].to(device=device, dtype=dtype).contiguous()
-        sizes = (self.nq * self.d, self.nkv * self.d, self.nkv * self.d)
-        if any((n + "_proj.bias") in tensors for n in ("q", "k", "v")):
-            parts = []
-            for n, size in zip(("q", "k", "v"), sizes):
+        q, kv = self.nq * self.d, self.nkv * self.d
+        has_bias = any((n + "_proj.bias") in tensors for n in ("q", "k", "v"))
+        layout = {"w_qkv": ((q + 2 * kv, self.hidden), dtype), "w_o": ((self.hidden, q), dtype)}
+        if has_bias:
+            layout["b_qkv"] = ((q + 2 * kv,), torch.float32)              # added in float32
+        self.buffers = buf = WeightBuffers(device, layout)
+        at = 0
+        for n, size in zip(("q", "k", "v"), (q, kv, kv)):                 # each projection into its rows of the stack
+            buf["w_qkv"][at:at + size].copy_(tensors[n + "_proj.weight"])
+            if has_bias:
                 b = tensors.get(n + "_proj.bias")
-                parts.append(torch.zeros(size, dtype=torch.float32, device=device) if b is None
-                             else b.to(device=device, dtype=torch.float32))
-            self.b_qkv = torch.cat(parts).contiguous()      # added in float32
-        else:
-            self.b_qkv = None
+                if b is None:
+                    buf["b_qkv"][at:at + size].zero_()
+                else:
+                    buf["b_qkv"][at:at + size].copy_(b)
+            at += size
+        buf["w_o"].copy_(tensors["o_proj.weight"])
+        self.w_qkv, self.w_o = buf["w_qkv"], buf["w_o"]
+        self.b_qkv = buf["b_qkv"] if has_bias else None
 
     def step_sections(self, ctx):
         """The work lists of the kernel table's attention kernels, if it has any."""

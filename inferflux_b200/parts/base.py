@@ -56,6 +56,40 @@ class RotaryTable:
     interleaved: bool            # False: (i, i + rotary_dim/2); True: (2i, 2i+1)
 
 
+# ------------------------------------------------------------------ weight storage
+
+class WeightBuffers:
+    """The tensors a part keeps, carved out of ONE device allocation at offsets that are
+    multiples of 256 bytes (TMA wants 16; 256 keeps every tensor on a fresh sector line).
+    The reference packs a whole model into one cudaMalloc with no padding
+    (runtime/backends/cuda/inferflux_cuda_executor.cpp:648-702); here each part packs its
+    own, and a stacked matrix is filled slice by slice from the file's tensors, so that no
+    second copy of it ever exists on the device.
+
+        buf = WeightBuffers(device, {"w_qkv": ((q + 2 * kv, h), dtype), "b_qkv": ((q + 2 * kv,), torch.float32)})
+        buf["w_qkv"][:q].copy_(tensors["q_proj.weight"])
+    """
+
+    ALIGN = 256
+
+    def __init__(self, device, layout: Dict[str, Tuple[Tuple[int, ...], torch.dtype]]):
+        offsets, total = {}, 0
+        for name, (shape, dtype) in layout.items():
+            n = torch.empty(0, dtype=dtype).element_size()
+            for d in shape:
+                n *= int(d)
+            offsets[name] = (total, n)
+            total += -(-n // self.ALIGN) * self.ALIGN
+        self.storage = torch.empty(total + self.ALIGN, dtype=torch.uint8, device=device)
+        shift = (-self.storage.data_ptr()) % self.ALIGN      # 0 on the GPU, whose allocator aligns to 512 bytes
+        self.views = {name: self.storage[shift + off:shift + off + n].view(layout[name][1]).view(layout[name][0])
+                      for name, (off, n) in offsets.items()}
+        self.nbytes = total
+
+    def __getitem__(self, name: str) -> torch.Tensor:
+        return self.views[name]
+
+
 # --------------------------------------------------------------------------- parts
 
 class Part:

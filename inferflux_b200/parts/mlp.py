@@ -6,7 +6,7 @@ from __future__ import annotations
 import torch
 
 from ..weights.loader import TensorSpec
-from .base import FeedForward, register_part
+from .base import FeedForward, WeightBuffers, register_part
 
 
 @register_part("ffn", "swiglu")
@@ -31,9 +31,12 @@ class SwiGLU(FeedForward):
         }
 
     def load(self, tensors, dtype, device):
-        self.w_gate_up = torch.cat([tensors["gate_proj.weight"].to(device=device, dtype=dtype),
-                                    tensors["up_proj.weight"].to(device=device, dtype=dtype)], dim=0).contiguous()
-        self.w_down = tensors["down_proj.weight"].to(device=device, dtype=dtype).contiguous()
+        self.buffers = buf = WeightBuffers(device, {"w_gate_up": ((2 * self.inter, self.hidden), dtype),
+                                                    "w_down": ((self.hidden, self.inter), dtype)})
+        buf["w_gate_up"][:self.inter].copy_(tensors["gate_proj.weight"])
+        buf["w_gate_up"][self.inter:].copy_(tensors["up_proj.weight"])
+        buf["w_down"].copy_(tensors["down_proj.weight"])
+        self.w_gate_up, self.w_down = buf["w_gate_up"], buf["w_down"]
 
     def forward(self, h, ctx):
         k = ctx.kernels

@@ -118,33 +118,60 @@ class _Staging:
             e.synchronize()
 
 
+class WeightSource:
+    """The checked tensors of a model folder, handed out a few at a time: `take(names)` brings
+    those tensors to the device (mapped file -> pinned buffers -> device), so that a model can be
+    loaded part by part and only one part's unpacked tensors ever exist beside the model."""
+
+    def __init__(self, model_dir, expected: Dict[str, TensorSpec], device="cpu",
+                 run_dtype: Optional[torch.dtype] = None):
+        self.shards = open_model_shards(model_dir)
+        self.expected = expected
+        self.device = torch.device(device)
+        self.run_dtype = run_dtype
+        self.staging = _Staging(self.device) if self.device.type == "cuda" else None
+        try:
+            self.owner = {}
+            for sh in self.shards:
+                for n in sh.names():
+                    self.owner.setdefault(n, sh)      # first occurrence of a name wins, as in the reference
+            check_tensors({n: sh.shape(n) for n, sh in self.owner.items()}, expected, where=str(model_dir))
+        except BaseException:
+            self.close()
+            raise
+
+    def names(self):
+        return [n for n, spec in self.expected.items() if n in self.owner and not spec.ignored]
+
+    def take(self, names) -> Dict[str, torch.Tensor]:
+        out = {}
+        for n in names:
+            if n not in self.owner or self.expected[n].ignored:
+                continue
+            if self.staging is None:
+                t = self.owner[n].tensor(n)
+                out[n] = t.to(stored_dtype(t.dtype, self.run_dtype))
+            else:
+                t = self.owner[n].view(n)
+                out[n] = self.staging.to_device(t).to(stored_dtype(t.dtype, self.run_dtype))
+                del t
+        if self.staging is not None:
+            self.staging.finish()
+        return out
+
+    def close(self):
+        for sh in self.shards:
+            sh.close()
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.close()
+
+
 def load_weights(model_dir, expected: Dict[str, TensorSpec], device="cpu",
                  run_dtype: Optional[torch.dtype] = None) -> Dict[str, torch.Tensor]:
-    """All tensors of a model folder that `expected` names, on `device`.  To a CUDA device the bytes go
-    from the mapped file through pinned buffers; the dtype is converted there."""
-    shards = open_model_shards(model_dir)
-    dev = torch.device(device)
-    staging = _Staging(dev) if dev.type == "cuda" else None
-    try:
-        owner = {}
-        for sh in shards:
-            for n in sh.names():
-                owner.setdefault(n, sh)          # first occurrence of a name wins, as in the reference
-        check_tensors({n: sh.shape(n) for n, sh in owner.items()}, expected, where=str(model_dir))
-        out = {}
-        for n, spec in expected.items():
-            if n not in owner or spec.ignored:
-                continue
-            if staging is None:
-                t = owner[n].tensor(n)
-                out[n] = t.to(stored_dtype(t.dtype, run_dtype))
-            else:
-                t = owner[n].view(n)
-                out[n] = staging.to_device(t).to(stored_dtype(t.dtype, run_dtype))
-                del t
-        if staging is not None:
-            staging.finish()
-        return out
-    finally:
-        for sh in shards:
-            sh.close()
+    """All tensors of a model folder that `expected` names, on `device`."""
+    with WeightSource(model_dir, expected, device, run_dtype) as src:
+        return src.take(src.names())

@@ -75,3 +75,39 @@ def test_a_float16_file_in_a_32_bit_run_matches_the_plain_implementation(tmp_pat
     runner = ModelRunner(model, cuda_kernels, page_size=8, num_pages=8, max_seqs=2)
     got = runner.step([StepEntry("r", toks, list(range(len(toks))))]).double().cpu()
     assert float((got - want).abs().max()) < 1e-4
+
+
+def test_loading_never_holds_much_more_than_the_model(tmp_path):
+    """A folder of the 1.5B layer sizes (six layers, tied head) is loaded part by part: stacked matrices are
+    filled slice by slice in their final place, so the peak of device memory stays within a tenth of the
+    model's own bytes; every part's tensors sit in one allocation at offsets that are multiples of 256."""
+    from inferflux_b200.config import Qwen2Config
+    from inferflux_b200.models import expected_tensors, load_model
+    from inferflux_b200.weights import random_tensors, write_safetensors
+    import json
+    cfg = Qwen2Config(hidden_size=1536, num_hidden_layers=6, num_attention_heads=12, num_key_value_heads=2, head_dim=128,
+                      intermediate_size=8960, vocab_size=151936, tie_word_embeddings=True, max_position_embeddings=1024)
+    W = random_tensors(expected_tensors(cfg.to_plan()), 3, dtype=torch.bfloat16, device="cuda:0")
+    write_safetensors(tmp_path / "model.safetensors", {n: t.cpu() for n, t in W.items()}, metadata={"format": "pt"})
+    (tmp_path / "config.json").write_text(json.dumps(cfg.to_dict()))
+    model_bytes = sum(t.numel() * t.element_size() for t in W.values())
+    probe = {n: W[n].clone() for n in ("model.layers.3.self_attn.k_proj.weight", "model.layers.5.mlp.up_proj.weight")}
+    del W
+    torch.cuda.empty_cache()
+    torch.cuda.synchronize()
+    base = torch.cuda.memory_allocated()
+    torch.cuda.reset_peak_memory_stats()
+    _c, model = load_model(tmp_path, dtype="bfloat16", device="cuda:0")
+    torch.cuda.synchronize()
+    peak = torch.cuda.max_memory_allocated() - base
+    held = torch.cuda.memory_allocated() - base
+    assert held <= 1.02 * model_bytes + (8 << 20), (held, model_bytes)       # norms and biases are kept in float32
+    assert peak <= 1.1 * model_bytes, f"peak {peak / 2**20:.0f} MiB for a model of {model_bytes / 2**20:.0f} MiB"
+    a = model.layers[3].mixer
+    q, kv = a.nq * a.d, a.nkv * a.d
+    assert torch.equal(a.w_qkv[q:q + kv], probe["model.layers.3.self_attn.k_proj.weight"])
+    f = model.layers[5].ffn
+    assert torch.equal(f.w_gate_up[f.inter:], probe["model.layers.5.mlp.up_proj.weight"])
+    for t in (a.w_qkv, a.w_o, a.b_qkv, f.w_gate_up, f.w_down):
+        assert t.data_ptr() % 256 == 0 and t.is_contiguous()
+    assert a.w_qkv.untyped_storage().data_ptr() == a.w_o.untyped_storage().data_ptr()      # one allocation a part
