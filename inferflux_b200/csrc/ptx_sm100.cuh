@@ -104,6 +104,34 @@ inline int make_tensor_map_bf16(CUtensorMap* map, const void* base, long long ro
   return r == CUDA_SUCCESS ? 0 : 2000 + (int)r;
 }
 
+// Tensor maps of weight matrices ([rows, cols] bfloat16, boxes of [box_rows, 64]), made once per tensor and kept.
+inline int weight_tensor_map(CUtensorMap* out, const void* base, long long rows, int cols, int box_rows) {
+  struct Key {
+    const void* base;
+    long long rows;
+    int cols, box;
+    bool operator==(const Key& o) const { return base == o.base && rows == o.rows && cols == o.cols && box == o.box; }
+  };
+  struct Hash {
+    size_t operator()(const Key& k) const {
+      return std::hash<const void*>()(k.base) ^ (size_t)k.rows * 1000003u ^ (size_t)k.cols * 7919u ^ (size_t)k.box;
+    }
+  };
+  static std::unordered_map<Key, CUtensorMap, Hash> cache;
+  static std::mutex mu;
+  std::lock_guard<std::mutex> lock(mu);
+  Key key{base, rows, cols, box_rows};
+  auto it = cache.find(key);
+  if (it == cache.end()) {
+    CUtensorMap m;
+    int rc = make_tensor_map_bf16(&m, base, rows, cols, box_rows);
+    if (rc) return rc;
+    it = cache.emplace(key, m).first;
+  }
+  *out = it->second;
+  return 0;
+}
+
 // Tensor maps of key/value pools (one per layer's pool, rows of one head's `d` elements, boxes of
 // 16 rows), made once and kept.
 inline int pool_tensor_map(CUtensorMap* out, const void* base, long long rows, int d) {

@@ -510,3 +510,19 @@ def test_penalties_and_bias(cuda_kernels):
     cuda_kernels.logit_bias(logits, rows, toks, bias)
     want[0, 3] += 1.5; want[1, 3] -= 2.0; want[1, 99] += 100.0
     close(logits.cpu(), want, atol=1e-6)
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 256, 64), (130, 520, 264), (257, 1000, 1536), (512, 4608, 3584), (300, 256, 8960)])
+def test_many_rows_tensor_core_product_and_its_swiglu(cuda_kernels, M, N, K):
+    """The tcgen05 product for prompt portions (128 x 256 tiles, persistent blocks, two accumulators in
+    tensor memory): plain store, and silu(gate) * up from stacked weights, at sizes with ragged edges."""
+    a = rnd(M, K, dtype=torch.bfloat16, seed=40, scale=0.5)
+    w = rnd(N, K, dtype=torch.bfloat16, seed=41, scale=0.1)
+    want = a.double() @ w.double().t()
+    tol = 1e-4 * math.sqrt(K)
+    close(cuda_kernels.linear_tiles(a, w), want, atol=tol, rtol=2 ** -8)
+    if N % 2 == 0:
+        half = N // 2
+        g, u = want[:, :half], want[:, half:]
+        close(cuda_kernels.linear_tiles(a, w, swiglu=True), g / (1 + torch.exp(-g)) * u, atol=tol, rtol=2 ** -7)
+    cuda_kernels.check_errors()
