@@ -450,7 +450,22 @@ def test_sampling_over_many_blocks_against_one_block(cuda_kernels, vocab):
     seed_lo = torch.arange(rows, dtype=torch.int32) + 77
     z = torch.zeros(rows, dtype=torch.int32)
     dev = lambda t: t.to(DEV)
-    agree = total = 0
+    from plain.plain_kernels import philox_uniform
+
+    def near_a_boundary(r, step, a, b):
+        """Two samplers may differ on a row only where float32 rounding decides: the draw falls within 2e-5 of
+        the total mass of a boundary between two kept tokens, or a token sits on a threshold."""
+        pr = torch.softmax(logits[r].cpu().double() / float(temperature[r]), -1)
+        keep = kept_mask(pr.float(), int(top_k[r]), float(top_p[r]), float(min_p[r]))
+        if not (bool(keep[a]) and bool(keep[b])):
+            edge = float(pr[keep].min())
+            return min(abs(float(pr[a]) - edge), abs(float(pr[b]) - edge)) <= 1e-3 * edge
+        c = torch.cumsum(torch.where(keep, pr, torch.zeros_like(pr)), 0)
+        target = philox_uniform(int(seed_lo[r]), 0, step) * float(c[-1])
+        lo, hi = min(a, b), max(a, b)
+        return float((c[lo:hi] - target).abs().min()) <= 2e-5 * float(c[-1])
+
+    plain = PlainKernels(wide=True)
     for step in range(8):
         st = torch.full((rows,), step, dtype=torch.int32)
         args = [dev(temperature), dev(top_k), dev(top_p), dev(min_p), dev(seed_lo), dev(z), dev(st)]
@@ -460,15 +475,17 @@ def test_sampling_over_many_blocks_against_one_block(cuda_kernels, vocab):
         few = cuda_kernels.sample(logits[:5].contiguous(), *[a[:5].contiguous() for a in args]).tolist()
         assert few == got[:5], "a row drew differently in a smaller batch"
         one = cuda_kernels.sample_one_block(logits, *args).tolist()
-        agree += sum(int(a == b) for a, b in zip(got, one))
-        total += rows
+        want = plain.sample(logits.cpu(), temperature, top_k, top_p, min_p, seed_lo, z, st).tolist()
+        for r in range(rows):                                 # against the one-block kernel and the plain statement
+            for other, name in ((one[r], "one-block kernel"), (want[r], "plain sampler")):
+                assert got[r] == other or (float(temperature[r]) > 0 and near_a_boundary(r, step, got[r], other)), \
+                    f"step {step} row {r}: drew {got[r]}, the {name} {other}"
         assert got[5] == int(torch.argmax(logits[5]))
         for r in range(rows):
             if float(temperature[r]) > 0:
                 p = torch.softmax(logits[r].cpu() / float(temperature[r]), -1)
                 keep = kept_mask(p, int(top_k[r]), float(top_p[r]), float(min_p[r]))
                 assert bool(keep[got[r]]) or float(p[got[r]]) >= 0.999 * float(p[keep].min()), (r, got[r])
-    assert agree >= total - 4, f"only {agree} of {total} draws agree with the one-block sampler"
     # filters the caller says nobody uses are not applied: the plain temperature draw
     plain = cuda_kernels.sample(logits, dev(temperature), dev(top_k), dev(top_p), dev(min_p * 0), dev(seed_lo), dev(z), dev(z),
                                 features=0).tolist()
