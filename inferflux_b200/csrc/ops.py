@@ -95,6 +95,33 @@ def _need(cond: bool, msg: str) -> None:
         raise KernelError(msg)
 
 
+_I, _F, _P, _LL = ctypes.c_int, ctypes.c_float, ctypes.c_void_p, ctypes.c_longlong
+
+
+class _StepArgs(ctypes.Structure):
+    """IfxStepArgs of csrc/layer_forward.cu: one step's batch, the same for every layer."""
+    _fields_ = ([(n, _I) for n in ("T", "num_decode", "num_tiles", "max_kv_len")]
+                + [(n, _P) for n in ("positions", "token_req", "req_slot", "decode_rows", "decode_meta", "prefill_tiles",
+                                     "norm_sumsq", "norm_tickets", "error_flag")]
+                + [(n, _I) for n in ("skinny_max_rows", "swiglu_tiles", "swiglu_tiles_max_k", "tensor_core_prefill")])
+
+
+class _LayerArgs(ctypes.Structure):
+    """IfxLayerArgs: one layer's sizes, constants, weights and cache."""
+    _fields_ = ([(n, _I) for n in ("hidden", "inter", "nq", "nkv", "d", "window", "rot", "interleaved")]
+                + [(n, _F) for n in ("scale", "eps_in", "eps_post")] + [("write_cache", _I)]
+                + [(n, _P) for n in ("norm_in_w", "norm_post_w", "b_qkv", "inv_freq", "w_qkv", "w_o", "w_gate_up", "w_down",
+                                     "kv_pool", "block_table")]
+                + [(n, _I) for n in ("max_blocks", "page_size", "num_pages", "pad0")])
+
+
+class _LayerIO(ctypes.Structure):
+    """IfxLayerIO: what changes from call to call, and what comes back."""
+    _fields_ = [("x", _P), ("pending_tensor", _P), ("pending_parts", _P), ("pending_splits", _I), ("parity", _I),
+                ("ws", _P), ("ws_bytes", _LL), ("out_tensor", _P), ("out_parts", _P), ("out_splits", _I),
+                ("launches", _I), ("library_calls", _I), ("pad0", _I)]
+
+
 class CudaKernels:
     """Kernel table on one CUDA device."""
 
@@ -133,6 +160,15 @@ class CudaKernels:
         self._argmax_idx = torch.zeros(256 * 32, dtype=torch.int32, device=self.device)
         self._argmax_tickets = torch.zeros(256, dtype=torch.int32, device=self.device)
         self.error_flag = torch.zeros(1, dtype=torch.int32, device=self.device)   # set by a kernel whose bounded wait ran out
+        # whole layers from native code (0: every part launches its kernels from Python, the general way)
+        self.native_layers = os.environ.get("INFERFLUX_B200_NATIVE_LAYER", "1") != "0"
+        self.lib.ifx_layer_forward.restype = ctypes.c_int
+        self.lib.ifx_layer_workspace_bytes.restype = ctypes.c_longlong
+        self._layer_ws, self._layer_ws_all, self._layer_views = None, [], {}
+        self._layer_io = _LayerIO()
+        self._layer_io_ref = ctypes.byref(self._layer_io)
+        self._layer_parity = 0
+        self.native_layer_calls = 0
 
     # ------------------------------------------------------------- elementwise
     def embed(self, table, token_ids, vocab):
@@ -383,6 +419,131 @@ class CudaKernels:
                                          _DT[out_dtype], _stream()), "gemm_generic")
         self.launches += 1
         return out
+
+    # ------------------------------------------------------------ whole layers
+    def _native_parts(self, block):
+        """The block's (mixer, ffn, norm before the mixer, norm before the ffn) if it is exactly the arrangement
+        and the parts that csrc/layer_forward.cu runs (no subclass: one may have changed a forward), else None."""
+        known = getattr(block, "_native_parts", False)
+        if known is not False:
+            return known
+        from ..parts.attention import Attention
+        from ..parts.block import PreNormBlock
+        from ..parts.mlp import SwiGLU
+        from ..parts.norm import RMSNorm
+        parts = None
+        if type(block) is PreNormBlock:
+            m, f, n1, n2 = block.mixer, block.ffn, block.norm_mixer, block.norm_ffn
+            if (type(m) is Attention and type(f) is SwiGLU and type(n1) is RMSNorm and type(n2) is RMSNorm
+                    and m.hidden == f.hidden == n1.size == n2.size):
+                parts = (m, f, n1, n2)
+        block._native_parts = parts
+        block._native_layers = {}
+        return parts
+
+    def _native_workspace(self, T, parts):
+        m, f = parts[0], parts[1]
+        need = int(self.lib.ifx_layer_workspace_bytes(T, m.hidden, m.nq * m.d, m.nkv * m.d, f.inter, self.SKINNY_MAX_ROWS))
+        ws = self._layer_ws
+        if ws is None or ws.numel() < need:
+            if torch.cuda.is_current_stream_capturing():
+                return None                              # no allocation inside a graph: the parts run one by one
+            # graphs captured earlier hold the old one's address: it stays alive
+            ws = torch.empty(max(need, 2 * (0 if ws is None else ws.numel())), dtype=torch.uint8, device=self.device)
+            self._layer_ws_all.append(ws)
+            self._layer_ws = ws
+            self._layer_views = {}
+        return ws
+
+    def fused_prenorm_layer(self, block, x, pending, ctx, cache):
+        """One native call for a pre-norm layer of attention and SwiGLU in bfloat16: the kernels that the parts
+        would launch one by one, chosen by the same rules, launched from csrc/layer_forward.cu.  Returns
+        (x, the layer's last delta, unadded) or None if this block, dtype or cache is not what that code runs."""
+        if not self.native_layers or ctx.dtype is not torch.bfloat16 or cache.kv is None or cache.block_table is None:
+            return None
+        parts = self._native_parts(block)
+        if parts is None or x.dtype is not torch.float32:
+            return None
+        m, f, n1, n2 = parts
+        if block.mixer is not m or block.ffn is not f or block.norm_mixer is not n1 or block.norm_ffn is not n2:
+            block._native_parts = False                  # a part was exchanged: look again
+            return self.fused_prenorm_layer(block, x, pending, ctx, cache)
+        T = ctx.num_tokens
+        ws = self._native_workspace(T, parts)
+        if ws is None:
+            return None
+        tensors = (m.w_qkv, m.w_o, m.b_qkv, f.w_gate_up, f.w_down, n1.weight, n2.weight)
+        kv, table = cache.kv, cache.block_table
+        kv_ptr = kv.data_ptr()
+        # everything of the cache that the layer's structure holds: another runner may get the same addresses
+        key = (kv_ptr, table.data_ptr(), cache.writes, cache.page_size, table.shape[1], kv.shape[0])
+        entry = block._native_layers.get(key)
+        if entry is None or any(a is not b for a, b in zip(entry[1], tensors)):
+            if kv.dtype is not torch.bfloat16 or m.w_qkv.dtype is not torch.bfloat16:
+                return None
+            rotary = m.position.rotary(ctx.device) if m.position is not None else None
+            la = _LayerArgs(
+                hidden=m.hidden, inter=f.inter, nq=m.nq, nkv=m.nkv, d=m.d, window=int(m.window or 0),
+                rot=0 if rotary is None else int(rotary.rotary_dim),
+                interleaved=int(bool(rotary.interleaved)) if rotary is not None else 0,
+                scale=m.scale, eps_in=n1.eps, eps_post=n2.eps, write_cache=int(bool(cache.writes)),
+                norm_in_w=n1.weight.data_ptr(), norm_post_w=n2.weight.data_ptr(),
+                b_qkv=0 if m.b_qkv is None else m.b_qkv.data_ptr(),
+                inv_freq=0 if rotary is None else rotary.inv_freq.data_ptr(),
+                w_qkv=m.w_qkv.data_ptr(), w_o=m.w_o.data_ptr(), w_gate_up=f.w_gate_up.data_ptr(),
+                w_down=f.w_down.data_ptr(), kv_pool=kv_ptr, block_table=table.data_ptr(),
+                max_blocks=table.shape[1], page_size=cache.page_size, num_pages=kv.shape[0])
+            entry = (la, tensors, rotary, table, ctypes.byref(la))
+            if len(block._native_layers) >= 8:           # caches come and go with their runners
+                block._native_layers.clear()
+            block._native_layers[key] = entry
+        step = getattr(ctx, "_native_step", None)
+        if step is None or step[1] is not ctx.positions or step[0].max_kv_len != ctx.max_kv_len:
+            if "attn.prefill_tiles" not in ctx.extra:      # a step context built without the mixer as a provider
+                for name, vals in self.attention_sections(ctx).items():
+                    ctx.extra[name] = torch.tensor(vals, dtype=torch.int32, device=x.device)
+                    ctx.extra_len[name] = len(vals)
+            sa = _StepArgs(
+                T=T, num_decode=ctx.extra_len["attn.decode_rows"], num_tiles=ctx.extra_len["attn.prefill_tiles"] // 4,
+                max_kv_len=int(ctx.max_kv_len), positions=ctx.positions.data_ptr(), token_req=ctx.token_req.data_ptr(),
+                req_slot=ctx.req_slot.data_ptr(), decode_rows=ctx.extra["attn.decode_rows"].data_ptr(),
+                decode_meta=ctx.extra["attn.decode_meta"].data_ptr(),
+                prefill_tiles=ctx.extra["attn.prefill_tiles"].data_ptr(), norm_sumsq=self._norm_sumsq.data_ptr(),
+                norm_tickets=self._norm_tickets.data_ptr(), error_flag=self.error_flag.data_ptr(),
+                skinny_max_rows=self.SKINNY_MAX_ROWS, swiglu_tiles=int(self.swiglu_tiles),
+                swiglu_tiles_max_k=self.SWIGLU_TILES_MAX_K, tensor_core_prefill=int(self.tensor_core_prefill))
+            step = ctx._native_step = (sa, ctx.positions, ctypes.byref(sa))
+        io = self._layer_io
+        io.x = x.data_ptr()
+        if pending is None:
+            io.pending_tensor, io.pending_parts, io.pending_splits = 0, 0, 0
+        elif isinstance(pending, PartialSum):
+            if tuple(pending.shape) != tuple(x.shape):
+                return None
+            io.pending_tensor, io.pending_parts, io.pending_splits = 0, pending.parts.data_ptr(), pending.splits
+        else:
+            if pending.dtype is not torch.bfloat16 or pending.shape != x.shape or not pending.is_contiguous():
+                return None
+            io.pending_tensor, io.pending_parts, io.pending_splits = pending.data_ptr(), 0, 0
+        parity = self._layer_parity = 1 - self._layer_parity
+        io.parity = parity
+        io.ws, io.ws_bytes = ws.data_ptr(), ws.numel()
+        rc = self.lib.ifx_layer_forward(step[2], entry[4], self._layer_io_ref, _stream())
+        self.launches += io.launches
+        self.library_calls += io.library_calls
+        self.native_layer_calls += 1
+        _check(rc, "layer (native)")
+        view = (T, m.hidden, parity, io.out_splits)
+        out = self._layer_views.get(view)
+        if out is None:
+            at = (io.out_parts or io.out_tensor) - ws.data_ptr()
+            if io.out_splits:
+                n = io.out_splits * T * m.hidden * 4
+                out = PartialSum(ws[at:at + n].view(torch.float32).view(io.out_splits, T, m.hidden), torch.bfloat16)
+            else:
+                out = ws[at:at + T * m.hidden * 2].view(torch.bfloat16).view(T, m.hidden)
+            self._layer_views[view] = out
+        return x, out
 
     # --------------------------------------------------------------- attention
     PREFILL_TILE = 256         # query rows per work item of the prompt-portion attention kernels

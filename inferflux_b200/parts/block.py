@@ -12,6 +12,11 @@ class PreNormBlock(Block):
     sub_parts = {"norm_mixer": "norm", "mixer": "mixer", "norm_ffn": "norm", "ffn": "ffn"}
 
     def forward(self, x, pending, ctx, cache):
+        fused = getattr(ctx.kernels, "fused_prenorm_layer", None)    # a kernel table may run the whole layer itself
+        if fused is not None:
+            done = fused(self, x, pending, ctx, cache)
+            if done is not None:
+                return done
         h = self.norm_mixer.forward(x, pending, ctx, lazy=self.mixer.takes_scaled_rows)   # x += pending; h = norm(x)
         a = self.mixer.forward(h, ctx, cache)
         h = self.norm_ffn.forward(x, a, ctx, lazy=self.ffn.takes_scaled_rows)             # x += a; h = norm(x)
