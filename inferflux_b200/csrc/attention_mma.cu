@@ -572,7 +572,6 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap pool_map, const bf16*
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int item = blockIdx.x, g = blockIdx.y, split = blockIdx.z, num_splits = gridDim.z;
   const int G = nq / nkv;
-  pdl_launch_dependents();
   if (tid == 0) {
     for (int i = 0; i < 4 * STAGES; ++i) mbar_init(smem_addr(bars + i), 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -736,6 +735,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap pool_map, const bf16*
     }
     __syncwarp();
   }
+  pdl_launch_dependents();                 // the keys are read: the output projection may fetch its weights now
   if (!ok) {
     if (lane == 0) atomicExch(error_flag, 4);
     // copies that were issued and not waited for must land before the block leaves

@@ -34,10 +34,25 @@ __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;"
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 extern int g_pdl_enabled;      // 1: launch_pdl sets the programmatic-serialization attribute
+extern int g_shared_carveout;  // >= 0: percent of the SM's memory every launch_pdl kernel prefers as shared memory
 
 template <typename... KArgs, typename... Args>
 inline int launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
                       int cluster_z, Args... args) {
+  if (g_shared_carveout >= 0) {
+    // Every kernel of the chain asks for the same split of the SM's memory into shared memory and L1, so that
+    // no SM has to drain to change it between two kernels (measured: 3.30 -> 3.23 ms for a decode step of the
+    // 7B shape at batch 8 with 100, 3.87 ms with 50).
+    static const void* configured[64];                   // kernels of this signature seen so far
+    static int num_configured = 0;
+    const void* fn = reinterpret_cast<const void*>(kernel);
+    bool seen = false;
+    for (int i = 0; i < num_configured; ++i) seen = seen || configured[i] == fn;
+    if (!seen) {
+      cudaFuncSetAttribute(fn, cudaFuncAttributePreferredSharedMemoryCarveout, g_shared_carveout);
+      if (num_configured < 64) configured[num_configured++] = fn;
+    }
+  }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
   cfg.blockDim = block;

@@ -6,6 +6,7 @@
 namespace ifx {
 
 int g_pdl_enabled = 1;
+int g_shared_carveout = 100;
 
 // ------------------------------------------------------------------ embedding
 // out[t, :] = table[token[t], :] widened to float32.  A token id outside the
@@ -433,6 +434,12 @@ using namespace ifx;
 extern "C" {
 
 // 1 (default): kernels of the decode chain overlap their start with the previous kernel's end.
+// Percent of an SM's memory the chain's kernels prefer as shared memory (-1: leave it to the driver).
+int ifx_set_shared_carveout(int percent) {
+  g_shared_carveout = percent;
+  return 0;
+}
+
 int ifx_set_pdl(int enabled) {
   g_pdl_enabled = enabled ? 1 : 0;
   return 0;

@@ -144,6 +144,8 @@ class CudaKernels:
         self.lib.ifx_sample_scratch_bytes.restype = ctypes.c_longlong
         with torch.cuda.device(self.device):
             _check(self.lib.ifx_cublas_init(), "cublas init")
+        if os.environ.get("INFERFLUX_B200_CARVEOUT", "") != "":    # for measurements: -1 leaves the split to the driver
+            self.lib.ifx_set_shared_carveout(int(os.environ["INFERFLUX_B200_CARVEOUT"]))
         if os.environ.get("INFERFLUX_B200_PDL", "1") == "0":      # for measurements: no overlap of consecutive kernels
             self.lib.ifx_set_pdl(0)
         # prompt portions on the tcgen05 attention kernel (0: the mma.sync kernel, for comparisons)

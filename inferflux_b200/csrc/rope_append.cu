@@ -23,7 +23,8 @@ __global__ void rope_append_kernel(const T* __restrict__ qkv, const float* __res
                                    const int* __restrict__ req_slot, const int* __restrict__ block_table,
                                    int max_blocks, int page_size, int num_pages, T* __restrict__ kv_pool,
                                    T* __restrict__ q_out, int nq, int nkv, int d, int write_cache) {
-  pdl_launch_dependents();
+  // No early pdl_launch_dependents() here: the attention kernel behind this one would only sit on its shared
+  // memory while the q/k/v product in front is still running (measured on the layer's chain: 106.7 -> 103.7 us).
   // Positions, slots, the block table, the bias and the angles do not come from the kernel in front:
   // they are fetched and the sines computed before it is known to have finished.
   const int t = blockIdx.x;
