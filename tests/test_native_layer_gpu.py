@@ -58,6 +58,29 @@ def test_real_layer_sizes_native_layers_equal_parts_one_by_one(shape, rows, cuda
             assert np.array_equal(parts[rid], native[rid]), f"{shape}/{rid}: {np.abs(parts[rid] - native[rid]).max()}"
 
 
+def test_native_layers_beside_layers_of_other_parts(cuda_kernels, monkeypatch):
+    """A model whose schedule runs the framework's attention layer, then a layer of the tests' own parts (a mixer
+    with state, a routed feed-forward), then the attention layer again: the first and the last run natively,
+    the middle one part by part, and the unadded delta passes between them in both directions."""
+    import test_parts_gpu as toys
+    from inferflux_b200.models import Model
+    from inferflux_b200.weights import random_tensors
+    toys._register_toys()
+    H, V, I = 64, 300, 96
+    model = Model(toys._toy_plan(H, V, I))
+    tensors = random_tensors(model.expected_tensors(), seed=3, dtype=torch.float32, std=0.08, norm_jitter=0.1)
+    tensors["model.embed_tokens.weight"] *= 10
+    model.load(tensors, torch.bfloat16, "cuda:0")
+    reqs = {f"r{i}": helpers.random_tokens(V, n, 200 + i) for i, n in enumerate([40, 33, 50])}
+    for make_trace in (helpers.trace_whole, helpers.trace_portions, lambda r: helpers.trace_mixed(r, 192)):
+        steps = make_trace(reqs)
+        parts, none = run(model, cuda_kernels, steps, V, False, monkeypatch, page_size=8, num_pages=24)
+        native, calls = run(model, cuda_kernels, steps, V, True, monkeypatch, page_size=8, num_pages=24)
+        assert none == 0 and calls > 0 and calls % 2 == 0          # two of the three schedule entries a step
+        for rid in reqs:
+            assert np.array_equal(parts[rid], native[rid]), f"{rid}: {np.abs(parts[rid] - native[rid]).max()}"
+
+
 def test_a_block_of_other_parts_is_left_to_its_parts(cuda_kernels):
     """The native code runs exactly one arrangement of exactly these parts: a subclass may have changed a forward."""
     from inferflux_b200.parts.attention import Attention
