@@ -17,7 +17,11 @@
 //                PARTIAL  part[split, m, n] = acc in float32, for consumers that add
 //                         the K slices themselves (residual + norm, bias + rotation),
 //                SWIGLU   two accumulators (gate rows and up rows of the same
-//                         outputs): out[m, n] = silu(gate) * up.
+//                         outputs): out[m, n] = silu(gate) * up,
+//                SWIGLU64 the same for a narrow product: 64 gate rows and 64 up rows share
+//                         one accumulator (lanes 0-63 and 64-127), so that twice as many
+//                         blocks stream the weights; the up half crosses to the gate half's
+//                         warps through shared memory.
 //
 // Splitting K gives narrow products (N = 3584) enough blocks to pull the full HBM
 // rate; the partial sums stay in L2 until the consumer reads them, in a fixed
@@ -37,7 +41,7 @@ namespace ifx {
 constexpr int kTileN = 128;       // weight rows per block (MMA M)
 constexpr int kTileK = 64;        // bf16 elements per k-block = one 128-byte swizzle row
 
-enum { MODE_STORE = 0, MODE_PARTIAL = 1, MODE_SWIGLU = 2 };
+enum { MODE_STORE = 0, MODE_PARTIAL = 1, MODE_SWIGLU = 2, MODE_SWIGLU64 = 3 };
 
 __device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr) {
   // K-major tile of 128-byte rows, 128-byte swizzle: 8-row groups 1024 bytes apart.
@@ -82,7 +86,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 2 * stages + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n0 = blockIdx.x * kTileN;
+  const int n0 = blockIdx.x * (MODE == MODE_SWIGLU64 ? kTileN / 2 : kTileN);
   const int split = blockIdx.y;
   const int total_kblocks = (K + kTileK - 1) / kTileK;
   const int kb0 = split * kblocks_per_split;
@@ -127,6 +131,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         const int kx = (kb0 + i) * kTileK;
         tma_load_2d_hint(dst, &map_w, kx, n0, bar, stream_once);
         if (MODE == MODE_SWIGLU) tma_load_2d_hint(dst + W_BYTES, &map_w, kx, up_row_offset + n0, bar, stream_once);
+        if (MODE == MODE_SWIGLU64) tma_load_2d_hint(dst + W_BYTES / 2, &map_w, kx, up_row_offset + n0, bar, stream_once);
       }
       pdl_wait();
       for (int i = 0; i < early; ++i)
@@ -143,6 +148,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         const int kx = (kb0 + i) * kTileK;
         tma_load_2d_hint(dst, &map_w, kx, n0, bar, stream_once);
         if (MODE == MODE_SWIGLU) tma_load_2d_hint(dst + W_BYTES, &map_w, kx, up_row_offset + n0, bar, stream_once);
+        if (MODE == MODE_SWIGLU64) tma_load_2d_hint(dst + W_BYTES / 2, &map_w, kx, up_row_offset + n0, bar, stream_once);
         tma_load_2d(dst + W_TILES * W_BYTES, &map_a, kx, 0, bar);
         issued = i + 1;
       }
@@ -182,7 +188,9 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
   } else {
     // ----------------------------------------------------------- epilogue
     const int quarter = warp & 3;                 // TMEM lanes this warp may read
-    const int n = n0 + quarter * 32 + lane;
+    // SWIGLU64: lanes 0-63 hold gate rows, lanes 64-127 the up rows of the same 64 outputs
+    const int n = MODE == MODE_SWIGLU64 ? n0 + (quarter & 1) * 32 + lane : n0 + quarter * 32 + lane;
+    const bool up_half = MODE == MODE_SWIGLU64 && quarter >= 2;
     pdl_wait();                                   // nothing is written before the kernel in front has finished
     // Rows that arrive pre-normed (x * w without the norm's row scale) get the scale here:
     // rsqrt(mean(x^2) + eps) from the per-chunk sums of squares the norm kernel left.
@@ -219,14 +227,27 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
 #pragma unroll
         for (int j = 0; j < 16; ++j) g[j] = u[j] = 0u;
       }
-      if (n < N) {
+      if (MODE == MODE_SWIGLU64) {
+        __shared__ float up_rows[64][17];                        // the up half of these 16 token columns
+        if (up_half) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) up_rows[(quarter & 1) * 32 + lane][j] = __uint_as_float(g[j]);
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (!up_half) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) u[j] = __float_as_uint(up_rows[(quarter & 1) * 32 + lane][j]);
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");         // read before the next round overwrites it
+      }
+      if (n < N && !up_half) {
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
           const int m = c + j;
           if (m >= M) break;
           const float rs = row_sumsq != nullptr ? row_scale[m] : 1.0f;
           float v = __uint_as_float(g[j]) * rs;
-          if (MODE == MODE_SWIGLU) {
+          if (MODE == MODE_SWIGLU || MODE == MODE_SWIGLU64) {
             const float up = __uint_as_float(u[j]) * rs;
             v = __fdividef(v, 1.0f + __expf(-v)) * up;       // a few float32 ulps, far below the bfloat16 rounding
           }
@@ -263,20 +284,31 @@ struct MapKeyHash {
 };
 
 // Weight maps are made once per weight tensor and kept.
-static int weight_map(CUtensorMap* out, const void* base, int rows, int cols) {
+static int weight_map(CUtensorMap* out, const void* base, int rows, int cols, int box_rows) {
   static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
   static std::mutex mu;
   std::lock_guard<std::mutex> lock(mu);
-  MapKey key{base, rows, cols, kTileN};
+  MapKey key{base, rows, cols, box_rows};
   auto it = cache.find(key);
   if (it == cache.end()) {
     CUtensorMap m;
-    int rc = make_tensor_map_bf16(&m, base, rows, cols, kTileN);
+    int rc = make_tensor_map_bf16(&m, base, rows, cols, box_rows);
     if (rc) return rc;
     it = cache.emplace(key, m).first;
   }
   *out = it->second;
   return 0;
+}
+
+static int sm_count() {
+  static int n = 0;
+  if (n == 0) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess ||
+        n <= 0)
+      n = 148;
+  }
+  return n;
 }
 
 static size_t skinny_smem_bytes(int npad, int mode, int stages) {
@@ -290,9 +322,13 @@ static int launch_skinny(const CUtensorMap& mw, const CUtensorMap& ma, const flo
                          int sumsq_chunks, float eps, int* error_flag, cudaStream_t stream) {
   const int total_kblocks = (K + kTileK - 1) / kTileK;
   const int per_split = (total_kblocks + splits - 1) / splits;
-  // as many stages as fit ~100 KB (two blocks per SM), at most the k-blocks of a split; SWIGLU blocks and blocks
-  // with 256 token rows (32 KB of activations a stage) own their SM
-  const size_t budget = (MODE == MODE_SWIGLU || NPAD == 256) ? 200 * 1024 : 100 * 1024;
+  // As many stages as fit the block's share of shared memory, at most the k-blocks of a split.  A grid of at most
+  // one block per SM gives every block the SM to itself; a larger one puts two on an SM so that all of them
+  // stream at once and share the HBM rate evenly, whatever the grid's remainder (27,648 / 128 = 216 tiles of a
+  // 32B-size gate/up product: 94 -> 83 us).  Blocks with 256 token rows (32 KB of activations a stage) own their SM.
+  dim3 grid((N + (MODE == MODE_SWIGLU64 ? kTileN / 2 : kTileN) - 1) / (MODE == MODE_SWIGLU64 ? kTileN / 2 : kTileN), splits);
+  const bool alone = NPAD == 256 || (long long)grid.x * grid.y <= sm_count();
+  const size_t budget = alone ? 200 * 1024 : (MODE == MODE_SWIGLU ? 110 * 1024 : 100 * 1024);
   int stages = 8;
   while (stages > 2 && skinny_smem_bytes(NPAD, MODE, stages) > budget) --stages;
   if (stages > per_split) stages = per_split < 2 ? 2 : per_split;
@@ -304,7 +340,6 @@ static int launch_skinny(const CUtensorMap& mw, const CUtensorMap& ma, const flo
     if (e != cudaSuccess) return (int)e;
     configured = smem;
   }
-  dim3 grid((N + kTileN - 1) / kTileN, splits);
   return launch_pdl(gemm_skinny_kernel<NPAD, MODE>, grid, dim3(192), smem, stream, 1, mw, ma, bias, out, partials, M, N,
                     K, per_split, up_row_offset, out_is_f32, stages, row_sumsq, sumsq_chunks, eps, error_flag);
 }
@@ -331,8 +366,10 @@ extern "C" int ifx_gemm_skinny(const void* act, const void* W, const float* bias
   if (mode == MODE_PARTIAL && partials == nullptr) return IFX_E_BADARG;
   const int total_kblocks = (K + kTileK - 1) / kTileK;
   if (splits > total_kblocks) return IFX_E_BADARG;
+  // a narrow gate/up product (at most half as many tiles as SMs): 64 + 64 weight rows a block
+  if (mode == MODE_SWIGLU && 2 * ((N + kTileN - 1) / kTileN) <= sm_count()) mode = MODE_SWIGLU64;
   CUtensorMap mw, ma;
-  int rc = weight_map(&mw, W, w_rows, K);
+  int rc = weight_map(&mw, W, w_rows, K, mode == MODE_SWIGLU64 ? kTileN / 2 : kTileN);
   if (rc) return rc;
   const int npad = M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : (M <= 128 ? 128 : 256)));
   rc = make_tensor_map_bf16(&ma, act, M, K, npad);
@@ -351,5 +388,6 @@ extern "C" int ifx_gemm_skinny(const void* act, const void* W, const float* bias
   if (mode == MODE_STORE) { BY_NPAD(MODE_STORE) }
   if (mode == MODE_PARTIAL) { BY_NPAD(MODE_PARTIAL) }
   if (mode == MODE_SWIGLU) { BY_NPAD(MODE_SWIGLU) }
+  if (mode == MODE_SWIGLU64) { BY_NPAD(MODE_SWIGLU64) }
   return IFX_E_BADARG;
 }
