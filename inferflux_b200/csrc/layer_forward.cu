@@ -23,7 +23,7 @@ int ifx_gemm_skinny(const void*, const void*, const float*, void*, float*, int, 
 int ifx_gemm_cublas_bf16(const void*, const void*, void*, int, int, int, int, cudaStream_t);
 int ifx_gemm_tcgen05(const void*, const void*, void*, int, int, int, int, int, int, int*, cudaStream_t);
 int ifx_rope_append(const void*, const float*, int, const float*, const float*, int, int, const int*, const int*, const int*,
-                    const int*, int, int, int, void*, void*, int, int, int, int, int, int, cudaStream_t);
+                    const int*, int, int, int, void*, void*, int, int, int, int, int, int, int, cudaStream_t);
 int ifx_attention_mma_supports(int);
 int ifx_attention_prefill_tcgen05_supports(int, int);
 int ifx_attention_prefill_tcgen05(const void*, int, const void*, const int*, const int*, const int*, void*, int, int, int, int,
@@ -112,6 +112,12 @@ inline int decode_splits(int tokens, int nkv, int max_keys, int max_splits) {
   while (s * 2 <= limit) s *= 2;
   if (s > 8 && tokens * nkv * s > 148) s = 8;
   return s;
+}
+
+// Whether the decode attention's grid is small enough to be let in early behind the rotation kernel
+// (CudaKernels.small_attention_grid).
+inline int small_attention_grid(int num_decode, int num_tiles, int nkv) {
+  return num_tiles == 0 && num_decode * nkv * 8 <= 148 ? 1 : 0;
 }
 
 struct Delta {               // a product's result on its way to the residual stream
@@ -257,7 +263,7 @@ extern "C" int ifx_layer_forward(const IfxStepArgs* s, const IfxLayerArgs* l, If
   if (!q || !attn) return IFX_E_TOOBIG;
   RUN(ifx_rope_append(qkv.tensor, qkv.parts, qkv.splits, l->b_qkv, l->inv_freq, l->rot, l->interleaved, s->positions,
                       s->token_req, s->req_slot, l->block_table, l->max_blocks, l->page_size, l->num_pages, l->kv_pool, q, T,
-                      nq, nkv, d, l->write_cache ? 1 : 0, IFX_DT_BF16, st));
+                      nq, nkv, d, l->write_cache ? 1 : 0, small_attention_grid(s->num_decode, s->num_tiles, nkv), IFX_DT_BF16, st));
 
   // ---- attention over the paged cache: prompt portions in one launch, single decoded tokens in another
   if (ifx_attention_mma_supports(d)) {

@@ -566,6 +566,15 @@ class CudaKernels:
             base += n
         return {"attn.decode_rows": rows, "attn.decode_meta": meta, "attn.prefill_tiles": tiles}
 
+    @staticmethod
+    def small_attention_grid(ctx, nkv):
+        """1 if the step is decoded tokens only and their attention grid (tokens x kv heads x up to 8 key slices)
+        leaves SMs free: the rotation kernel then lets it in early."""
+        extra_len = getattr(ctx, "extra_len", None) or {}
+        if "attn.decode_rows" not in extra_len:
+            return 0
+        return int(extra_len.get("attn.prefill_tiles", 0) == 0 and extra_len["attn.decode_rows"] * nkv * 8 <= 148)
+
     def rope_append(self, qkv, bias, rotary, nq, nkv, d, ctx, cache):
         """`qkv`: the stacked projections [T, (nq + 2 nkv) d] as a tensor or a PartialSum."""
         partial, splits = None, 0
@@ -589,7 +598,8 @@ class CudaKernels:
             int(bool(rotary.interleaved)) if rotary is not None else 0,
             _ptr(ctx.positions), _ptr(ctx.token_req), _ptr(ctx.req_slot), _ptr(table),
             0 if table is None else table.shape[1], cache.page_size, 0 if kv is None else kv.shape[0],
-            _ptr(kv), _ptr(q_out), T, nq, nkv, d, int(write), _DT[dtype], _stream()), "rope_append")
+            _ptr(kv), _ptr(q_out), T, nq, nkv, d, int(write), self.small_attention_grid(ctx, nkv), _DT[dtype],
+            _stream()), "rope_append")
         self.launches += 1
         return q_out
 
