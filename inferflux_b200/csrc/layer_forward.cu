@@ -48,6 +48,7 @@ struct IfxStepArgs {
   int* error_flag;
   // the kernel table's knobs
   int skinny_max_rows, swiglu_tiles, swiglu_tiles_max_k, tensor_core_prefill;
+  int overlap_attention, pad0;   // 1: a mixed step's two attention kernels run side by side on two streams
 };
 
 // One layer with one cache: filled once, when the layer first runs.
@@ -118,6 +119,27 @@ inline int decode_splits(int tokens, int nkv, int max_keys, int max_splits) {
 // (CudaKernels.small_attention_grid).
 inline int small_attention_grid(int num_decode, int num_tiles, int nkv) {
   return num_tiles == 0 && num_decode * nkv * 8 <= 148 ? 1 : 0;
+}
+
+// A second stream and two events per device, for the two attention kernels of a mixed step: the one over the
+// prompt portions (tensor-bound, few blocks) and the one over the single decoded tokens (HBM-bound) read the same
+// queries and write different rows, so neither has to wait for the other.
+struct SideStream {
+  cudaStream_t stream = nullptr;
+  cudaEvent_t fork = nullptr, join = nullptr;
+  bool ok = false;
+};
+inline SideStream* side_stream() {
+  static SideStream per_device[16];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 16) return nullptr;
+  SideStream& s = per_device[dev];
+  if (!s.stream) {
+    s.ok = cudaStreamCreateWithFlags(&s.stream, cudaStreamNonBlocking) == cudaSuccess &&
+           cudaEventCreateWithFlags(&s.fork, cudaEventDisableTiming) == cudaSuccess &&
+           cudaEventCreateWithFlags(&s.join, cudaEventDisableTiming) == cudaSuccess;
+  }
+  return s.ok ? &s : nullptr;
 }
 
 struct Delta {               // a product's result on its way to the residual stream
@@ -267,6 +289,18 @@ extern "C" int ifx_layer_forward(const IfxStepArgs* s, const IfxLayerArgs* l, If
 
   // ---- attention over the paged cache: prompt portions in one launch, single decoded tokens in another
   if (ifx_attention_mma_supports(d)) {
+    // both kinds in one step: the decoded tokens' kernel goes to the side stream, behind the rotation kernel
+    cudaStream_t decode_st = st;
+    SideStream* side = nullptr;
+    if (s->overlap_attention && s->num_tiles > 0 && s->num_decode > 0 && nq / nkv <= 16) {
+      cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
+      if (cudaStreamIsCapturing(st, &capturing) == cudaSuccess && capturing == cudaStreamCaptureStatusNone &&
+          (side = side_stream()) != nullptr) {
+        if (cudaEventRecord(side->fork, st) != cudaSuccess || cudaStreamWaitEvent(side->stream, side->fork, 0) != cudaSuccess)
+          return IFX_E_BADARG;
+        decode_st = side->stream;
+      }
+    }
     if (s->num_tiles > 0) {
       if (s->tensor_core_prefill && ifx_attention_prefill_tcgen05_supports(d, l->page_size))
         RUN(ifx_attention_prefill_tcgen05(q, T, l->kv_pool, l->block_table, s->prefill_tiles, s->req_slot, attn, s->num_tiles,
@@ -287,9 +321,12 @@ extern "C" int ifx_layer_forward(const IfxStepArgs* s, const IfxLayerArgs* l, If
         const int splits = decode_splits(s->num_decode, nkv, max_keys, ifx_attention_decode_max_splits(d, l->page_size));
         RUN(ifx_attention_decode_bf16(q, l->kv_pool, l->block_table, s->decode_meta, attn, s->num_decode, nq, nkv, d,
                                       l->page_size, l->max_blocks, l->num_pages, l->window, l->scale, splits, max_keys,
-                                      s->error_flag, st));
+                                      s->error_flag, decode_st));
       }
     }
+    if (decode_st != st &&
+        (cudaEventRecord(side->join, decode_st) != cudaSuccess || cudaStreamWaitEvent(st, side->join, 0) != cudaSuccess))
+      return IFX_E_BADARG;
   } else {
     RUN(ifx_attention_generic(q, l->kv_pool, l->block_table, s->positions, s->token_req, s->req_slot, nullptr, attn, T, nq,
                               nkv, d, l->page_size, l->max_blocks, l->num_pages, l->window, l->scale, IFX_DT_BF16, st));

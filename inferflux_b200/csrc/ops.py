@@ -103,7 +103,8 @@ class _StepArgs(ctypes.Structure):
     _fields_ = ([(n, _I) for n in ("T", "num_decode", "num_tiles", "max_kv_len")]
                 + [(n, _P) for n in ("positions", "token_req", "req_slot", "decode_rows", "decode_meta", "prefill_tiles",
                                      "norm_sumsq", "norm_tickets", "error_flag")]
-                + [(n, _I) for n in ("skinny_max_rows", "swiglu_tiles", "swiglu_tiles_max_k", "tensor_core_prefill")])
+                + [(n, _I) for n in ("skinny_max_rows", "swiglu_tiles", "swiglu_tiles_max_k", "tensor_core_prefill",
+                                     "overlap_attention", "pad0")])
 
 
 class _LayerArgs(ctypes.Structure):
@@ -164,6 +165,8 @@ class CudaKernels:
         self.error_flag = torch.zeros(1, dtype=torch.int32, device=self.device)   # set by a kernel whose bounded wait ran out
         # whole layers from native code (0: every part launches its kernels from Python, the general way)
         self.native_layers = os.environ.get("INFERFLUX_B200_NATIVE_LAYER", "1") != "0"
+        # in a natively run layer of a mixed step, the two attention kernels side by side on two streams
+        self.overlap_attention = os.environ.get("INFERFLUX_B200_ATTENTION_OVERLAP", "1") != "0"
         self.lib.ifx_layer_forward.restype = ctypes.c_int
         self.lib.ifx_layer_workspace_bytes.restype = ctypes.c_longlong
         self._layer_ws, self._layer_ws_all, self._layer_views = None, [], {}
@@ -513,7 +516,8 @@ class CudaKernels:
                 prefill_tiles=ctx.extra["attn.prefill_tiles"].data_ptr(), norm_sumsq=self._norm_sumsq.data_ptr(),
                 norm_tickets=self._norm_tickets.data_ptr(), error_flag=self.error_flag.data_ptr(),
                 skinny_max_rows=self.SKINNY_MAX_ROWS, swiglu_tiles=int(self.swiglu_tiles),
-                swiglu_tiles_max_k=self.SWIGLU_TILES_MAX_K, tensor_core_prefill=int(self.tensor_core_prefill))
+                swiglu_tiles_max_k=self.SWIGLU_TILES_MAX_K, tensor_core_prefill=int(self.tensor_core_prefill),
+                overlap_attention=int(self.overlap_attention))
             step = ctx._native_step = (sa, ctx.positions, ctypes.byref(sa))
         io = self._layer_io
         io.x = x.data_ptr()
