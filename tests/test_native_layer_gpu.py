@@ -58,6 +58,34 @@ def test_real_layer_sizes_native_layers_equal_parts_one_by_one(shape, rows, cuda
             assert np.array_equal(parts[rid], native[rid]), f"{shape}/{rid}: {np.abs(parts[rid] - native[rid]).max()}"
 
 
+def test_a_captured_graph_outlives_the_growth_of_the_layer_workspace(monkeypatch):
+    """Decoding is captured into a CUDA graph while the layer workspace is small; a long prompt of another request
+    then makes the kernel table take a larger one; the graph, replayed afterwards, still finds the memory it was
+    captured with.  A kernel table of its own, so that the workspace starts empty."""
+    from inferflux_b200.config import Qwen2Config
+    from inferflux_b200.csrc import CudaKernels
+    from inferflux_b200.models import random_model
+    from test_real_shapes_gpu import SHAPES
+    kernels = CudaKernels("cuda:0")
+    cfg = Qwen2Config(num_hidden_layers=2, max_position_embeddings=2048, **SHAPES["1.5b"])
+    model = random_model(cfg, seed=5, dtype="bfloat16", device="cuda:0", norm_jitter=0.2)
+    a = helpers.random_tokens(cfg.vocab_size, 60, 1)
+    b = helpers.random_tokens(cfg.vocab_size, 900, 2)
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": a[:40], "want": [39]}], "end": []}]
+    for i in range(40, 50):                                 # first seen, captured, then replayed
+        steps.append({"step": len(steps), "entries": [{"id": "a", "tokens": [a[i]], "want": [0]}], "end": []})
+    steps.append({"step": len(steps), "entries": [{"id": "b", "tokens": b, "want": [0, 899]}], "end": ["b"]})
+    for i in range(50, 60):
+        steps.append({"step": len(steps), "entries": [{"id": "a", "tokens": [a[i]], "want": [0]}],
+                      "end": ["a"] if i == 59 else []})
+    parts, _ = run(model, kernels, steps, cfg.vocab_size, False, monkeypatch, num_pages=96, cuda_graphs=True)
+    assert kernels._layer_ws is None
+    native, calls = run(model, kernels, steps, cfg.vocab_size, True, monkeypatch, num_pages=96, cuda_graphs=True)
+    assert calls > 0 and len(kernels._layer_ws_all) >= 2, "the long prompt was meant to outgrow the first workspace"
+    for rid in ("a", "b"):
+        assert np.array_equal(parts[rid], native[rid]), f"{rid}: {np.abs(parts[rid] - native[rid]).max()}"
+
+
 def test_native_layers_beside_layers_of_other_parts(cuda_kernels, monkeypatch):
     """A model whose schedule runs the framework's attention layer, then a layer of the tests' own parts (a mixer
     with state, a routed feed-forward), then the attention layer again: the first and the last run natively,
