@@ -460,27 +460,14 @@ class CudaKernels:
             self._layer_views = {}
         return ws
 
-    def fused_prenorm_layer(self, block, x, pending, ctx, cache):
-        """One native call for a pre-norm layer of attention and SwiGLU in bfloat16: the kernels that the parts
-        would launch one by one, chosen by the same rules, launched from csrc/layer_forward.cu.  Returns
-        (x, the layer's last delta, unadded) or None if this block, dtype or cache is not what that code runs."""
-        if not self.native_layers or ctx.dtype is not torch.bfloat16 or cache.kv is None or cache.block_table is None:
-            return None
-        parts = self._native_parts(block)
-        if parts is None or x.dtype is not torch.float32:
-            return None
+    def _native_layer_args(self, block, parts, ctx, cache):
+        """The C structure of one layer with one cache (sizes, constants, weight and cache addresses), made when
+        the pair first runs and kept on the block; None if the cache or the weights are not bfloat16."""
         m, f, n1, n2 = parts
-        if block.mixer is not m or block.ffn is not f or block.norm_mixer is not n1 or block.norm_ffn is not n2:
-            block._native_parts = False                  # a part was exchanged: look again
-            return self.fused_prenorm_layer(block, x, pending, ctx, cache)
-        T = ctx.num_tokens
-        ws = self._native_workspace(T, parts)
-        if ws is None:
-            return None
         tensors = (m.w_qkv, m.w_o, m.b_qkv, f.w_gate_up, f.w_down, n1.weight, n2.weight)
         kv, table = cache.kv, cache.block_table
         kv_ptr = kv.data_ptr()
-        # everything of the cache that the layer's structure holds: another runner may get the same addresses
+        # everything of the cache that the structure holds: another runner may get the same addresses
         key = (kv_ptr, table.data_ptr(), cache.writes, cache.page_size, table.shape[1], kv.shape[0])
         entry = block._native_layers.get(key)
         if entry is None or any(a is not b for a, b in zip(entry[1], tensors)):
@@ -498,18 +485,24 @@ class CudaKernels:
                 w_qkv=m.w_qkv.data_ptr(), w_o=m.w_o.data_ptr(), w_gate_up=f.w_gate_up.data_ptr(),
                 w_down=f.w_down.data_ptr(), kv_pool=kv_ptr, block_table=table.data_ptr(),
                 max_blocks=table.shape[1], page_size=cache.page_size, num_pages=kv.shape[0])
-            entry = (la, tensors, rotary, table, ctypes.byref(la))
+            entry = (la, tensors, rotary, table, ctypes.byref(la))      # the tensors stay alive with the addresses
             if len(block._native_layers) >= 8:           # caches come and go with their runners
                 block._native_layers.clear()
             block._native_layers[key] = entry
+        return entry[4]
+
+    def _native_step_args(self, ctx, device):
+        """The C structure of the step's batch (metadata addresses, counts, this table's knobs), made at the
+        step's first layer and kept on the context."""
         step = getattr(ctx, "_native_step", None)
         if step is None or step[1] is not ctx.positions or step[0].max_kv_len != ctx.max_kv_len:
             if "attn.prefill_tiles" not in ctx.extra:      # a step context built without the mixer as a provider
                 for name, vals in self.attention_sections(ctx).items():
-                    ctx.extra[name] = torch.tensor(vals, dtype=torch.int32, device=x.device)
+                    ctx.extra[name] = torch.tensor(vals, dtype=torch.int32, device=device)
                     ctx.extra_len[name] = len(vals)
             sa = _StepArgs(
-                T=T, num_decode=ctx.extra_len["attn.decode_rows"], num_tiles=ctx.extra_len["attn.prefill_tiles"] // 4,
+                T=ctx.num_tokens, num_decode=ctx.extra_len["attn.decode_rows"],
+                num_tiles=ctx.extra_len["attn.prefill_tiles"] // 4,
                 max_kv_len=int(ctx.max_kv_len), positions=ctx.positions.data_ptr(), token_req=ctx.token_req.data_ptr(),
                 req_slot=ctx.req_slot.data_ptr(), decode_rows=ctx.extra["attn.decode_rows"].data_ptr(),
                 decode_meta=ctx.extra["attn.decode_meta"].data_ptr(),
@@ -519,6 +512,29 @@ class CudaKernels:
                 swiglu_tiles_max_k=self.SWIGLU_TILES_MAX_K, tensor_core_prefill=int(self.tensor_core_prefill),
                 overlap_attention=int(self.overlap_attention))
             step = ctx._native_step = (sa, ctx.positions, ctypes.byref(sa))
+        return step[2]
+
+    def fused_prenorm_layer(self, block, x, pending, ctx, cache):
+        """One native call for a pre-norm layer of attention and SwiGLU in bfloat16: the kernels that the parts
+        would launch one by one, chosen by the same rules, launched from csrc/layer_forward.cu.  Returns
+        (x, the layer's last delta, unadded) or None if this block, dtype or cache is not what that code runs."""
+        if not self.native_layers or ctx.dtype is not torch.bfloat16 or cache.kv is None or cache.block_table is None:
+            return None
+        parts = self._native_parts(block)
+        if parts is None or x.dtype is not torch.float32:
+            return None
+        m, f, n1, n2 = parts
+        if block.mixer is not m or block.ffn is not f or block.norm_mixer is not n1 or block.norm_ffn is not n2:
+            block._native_parts = False                  # a part was exchanged: look again
+            return self.fused_prenorm_layer(block, x, pending, ctx, cache)
+        T = ctx.num_tokens
+        ws = self._native_workspace(T, parts)
+        if ws is None:
+            return None
+        layer = self._native_layer_args(block, parts, ctx, cache)
+        if layer is None:
+            return None
+        step = self._native_step_args(ctx, x.device)
         io = self._layer_io
         io.x = x.data_ptr()
         if pending is None:
@@ -534,7 +550,7 @@ class CudaKernels:
         parity = self._layer_parity = 1 - self._layer_parity
         io.parity = parity
         io.ws, io.ws_bytes = ws.data_ptr(), ws.numel()
-        rc = self.lib.ifx_layer_forward(step[2], entry[4], self._layer_io_ref, _stream())
+        rc = self.lib.ifx_layer_forward(step, layer, self._layer_io_ref, _stream())
         self.launches += io.launches
         self.library_calls += io.library_calls
         self.native_layer_calls += 1
