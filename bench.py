@@ -453,6 +453,8 @@ def main() -> int:
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--context", type=int, default=CONTEXT,
+                    help="tokens per request at the last timed decode step (default: the headline's 4,096)")
     ap.add_argument("--layers", type=int, default=0, help="run fewer layers than the shape has (named in config)")
     ap.add_argument("--shape", default="7b", choices=sorted(SHAPES), help="model shape (default: the 7B headline shape)")
     ap.add_argument("--timed-seconds", type=float, default=0.5,
@@ -478,6 +480,9 @@ def main() -> int:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
     warmup, steps = max(3, args.warmup), max(1, args.steps)
+    context = args.context
+    if context != CONTEXT:          # another context length: the headline's other points and checks do not apply
+        args.no_points = args.no_check = args.no_extras = True
 
     import torch
 
@@ -514,14 +519,15 @@ def main() -> int:
         return 0
 
     # how often the K-step loop is repeated: about --timed-seconds at the rate the bytes allow
-    est_ms = (weight_bytes(cfg, args.batch) + args.batch * CONTEXT * kv_bytes_per_token(cfg)) / (0.7 * pk["hbm_gbs"] * 1e6)
+    est_ms = (weight_bytes(cfg, args.batch) + args.batch * context * kv_bytes_per_token(cfg)) / (0.7 * pk["hbm_gbs"] * 1e6)
     repeats = max(1, min(12, int(-(-args.timed_seconds * 1000.0 // (steps * est_ms)))))
     biggest = max(args.batch, 1 if args.no_points else 64)
-    longest = CONTEXT + 4 * (warmup + repeats * steps) + 8 + biggest   # a prompt plus the most new tokens time_decode allows
+    longest = context + 4 * (warmup + repeats * steps) + 8 + biggest   # a prompt plus the most new tokens time_decode allows
+    cfg.max_position_embeddings = max(cfg.max_position_embeddings, longest)
     engine = _engine(cfg, page, biggest, longest)
 
     clock = ClockSampler()
-    main_run = time_decode(engine, cfg, args.batch, steps, warmup, repeats=repeats, clock=clock)
+    main_run = time_decode(engine, cfg, args.batch, steps, warmup, repeats=repeats, context=context, clock=clock)
     dev_ms = main_run["dev_ms"]
     value = args.batch * 1000.0 / dev_ms
     step_bytes = weight_bytes(cfg, args.batch) + args.batch * main_run["ctx"] * kv_bytes_per_token(cfg)
@@ -554,14 +560,14 @@ def main() -> int:
 
     checked = None
     if not args.no_check:
-        checked = {"b%d" % args.batch: check_logits(engine, cfg, args.batch, CONTEXT, rows=[0, args.batch - 1])}
+        checked = {"b%d" % args.batch: check_logits(engine, cfg, args.batch, context, rows=[0, args.batch - 1])}
         if not args.no_points:
-            checked["b64"] = check_logits(engine, cfg, 64, CONTEXT, rows=[0, 37])
+            checked["b64"] = check_logits(engine, cfg, 64, context, rows=[0, 37])
 
     baselines = None
     if not args.no_extras:
         from baseline.torch_plain import time_torch_plain
-        dec_ms, pre_ms = time_torch_plain(engine.model, cfg.vocab_size, args.batch, CONTEXT, PREFILL_TOKENS)
+        dec_ms, pre_ms = time_torch_plain(engine.model, cfg.vocab_size, args.batch, context, PREFILL_TOKENS)
         baselines = {"torch_plain": {"what": "the same weights in plain PyTorch (matmul + scaled_dot_product_attention, "
                                              "contiguous cache, eager)", "decode_tok_s": round(args.batch * 1000.0 / dec_ms, 1),
                                      "decode_ms_per_step": round(dec_ms, 3), "prefill_tok_s": round(PREFILL_TOKENS * 1000.0 / pre_ms, 1),
@@ -572,7 +578,7 @@ def main() -> int:
         del engine
         torch.cuda.empty_cache()
         small = qwen7b_config("1.5b")
-        eng = _engine(small, page, 64, CONTEXT + 4 * (5 + 2 * 20) + 80, chunk=512)
+        eng = _engine(small, page, 64, context + 4 * (5 + 2 * 20) + 80, chunk=512)
         r = time_decode(eng, small, 8, 20, 5, repeats=4, e2e=False)
         b15 = weight_bytes(small, 8) + 8 * r["ctx"] * kv_bytes_per_token(small)
         points["decode_b8_1p5b"] = round(8 * 1000.0 / r["dev_ms"], 1)
@@ -591,7 +597,7 @@ def main() -> int:
                    "hidden": cfg.hidden_size, "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads,
                    "head_dim": cfg.head_dim, "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size,
                    "rope_theta": cfg.rope_theta, "rms_norm_eps": cfg.rms_norm_eps, "global_batch": args.batch,
-                   "seq_len": CONTEXT, "context_at_timing": main_run["ctx"], "kv_page": page, "parallelism": "single GPU",
+                   "seq_len": context, "context_at_timing": main_run["ctx"], "kv_page": page, "parallelism": "single GPU",
                    "l2": "inputs larger than L2 (GBs of weights per step), no flush",
                    "peaks": pk["source"]},
         "repeats": repeats, "repeat_ms": [round(m, 4) for m in main_run["repeat_ms"]], "repeat_sm_mhz": repeat_clocks,

@@ -829,12 +829,11 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap pool_map, const bf16*
   cluster.sync();
 }
 
-template <int D>
-int launch_decode_tma(const CUtensorMap& pool_map, const bf16* q, const int* block_table, const int4* decode_meta,
-                      bf16* out, int num_items, int nq, int nkv, int page_size, int page_shift, int max_blocks,
-                      int num_pages, int window, float scale_log2, int num_splits, int max_keys, int* error_flag,
-                      cudaStream_t stream) {
-  constexpr int STAGES = D <= 128 ? 3 : 2;
+template <int D, int STAGES>
+int launch_decode_tma_stages(const CUtensorMap& pool_map, const bf16* q, const int* block_table, const int4* decode_meta,
+                             bf16* out, int num_items, int nq, int nkv, int page_size, int page_shift, int max_blocks,
+                             int num_pages, int window, float scale_log2, int num_splits, int max_keys, int* error_flag,
+                             cudaStream_t stream) {
   constexpr int stage_bytes = 4 * STAGES * 2 * 16 * D * 2;
   constexpr int merge_bytes = (4 * 16 * D + 2 * 4 * 16) * 4;
   constexpr int fin_bytes = (16 * D + 32) * 4;
@@ -862,6 +861,26 @@ int launch_decode_tma(const CUtensorMap& pool_map, const bf16* q, const int* blo
   return launch_pdl(attn_decode_tma_kernel<D, STAGES>, dim3(num_items, nkv, num_splits), dim3(128), (size_t)smem, stream,
                     num_splits, pool_map, q, block_table, decode_meta, out, nq, nkv, page_size, page_shift, max_blocks,
                     num_pages, window, scale_log2, tbl_cap, error_flag);
+}
+
+// Three 16-key tiles in flight a warp (96 KB a block at head size 128) feed the HBM when two blocks sit on every
+// SM.  A grid of at most one block per SM with long key ranges (one or two tokens at tens of thousands of keys) is
+// bound by what a block keeps in flight instead: it gets rings twice as deep.
+template <int D>
+int launch_decode_tma(const CUtensorMap& pool_map, const bf16* q, const int* block_table, const int4* decode_meta,
+                      bf16* out, int num_items, int nq, int nkv, int page_size, int page_shift, int max_blocks,
+                      int num_pages, int window, float scale_log2, int num_splits, int max_keys, int* error_flag,
+                      cudaStream_t stream) {
+  constexpr int BASE = D <= 128 ? 3 : 2;
+  const long long blocks = (long long)num_items * nkv * num_splits;
+  const int keys_per_warp = max_keys / (num_splits > 0 ? num_splits : 1) / 4;
+  if (D <= 128 && blocks <= 148 && keys_per_warp >= 16 * 4 * BASE)
+    return launch_decode_tma_stages<D, 2 * BASE>(pool_map, q, block_table, decode_meta, out, num_items, nq, nkv, page_size,
+                                                 page_shift, max_blocks, num_pages, window, scale_log2, num_splits, max_keys,
+                                                 error_flag, stream);
+  return launch_decode_tma_stages<D, BASE>(pool_map, q, block_table, decode_meta, out, num_items, nq, nkv, page_size,
+                                           page_shift, max_blocks, num_pages, window, scale_log2, num_splits, max_keys,
+                                           error_flag, stream);
 }
 
 template <int D>

@@ -327,6 +327,27 @@ def test_attention_decode_one_token_over_a_cluster_of_sixteen(cuda_kernels, nq, 
     cuda_kernels.check_errors()
 
 
+@pytest.mark.parametrize("nq,nkv,d,page,window", [(14, 2, 128, 16, None), (6, 1, 64, 32, None), (7, 1, 128, 16, 12500)])
+def test_attention_decode_one_token_over_thirteen_thousand_keys(cuda_kernels, nq, nkv, d, page, window):
+    """One decoded token far into a long context: few blocks, each with hundreds of keys a warp, which is where
+    the decode kernel runs with rings twice as deep.  The planted key may lie anywhere in the range."""
+    dtype = torch.bfloat16
+    lens, spans = [13000], [1]
+    ctx, cache, slots = make_cache_case(dtype, nkv, d, page, lens, spans, num_pages=-(-lens[0] // page) + 3, seed=33)
+    stored = fill_cache(cache, lens, slots, nkv, d, dtype, seed=34)
+    scale = 1.0 / math.sqrt(d)
+    pos = lens[0] - 1
+    first = max(0, pos - window + 1) if window else 0
+    for target in (first, pos, first + 17, first + (pos - first) // 3, pos - 1, first + (pos - first) * 11 // 16):
+        q = rnd(1, nq, d, dtype=dtype, seed=35, scale=0.3)
+        for h in range(nq):
+            q[0, h] = (stored[0][0][target, h // (nq // nkv)].float() * (12.0 / math.sqrt(d))).to(dtype).to(DEV)
+        want = attention_oracle(q, stored, lens, spans, nq, nkv, d, window, scale)
+        got = cuda_kernels.attention(q.view(1, nq * d), nq, nkv, d, window, scale, ctx, cache)
+        close(got.cpu(), want, atol=2e-2, rtol=2e-2)
+    cuda_kernels.check_errors()
+
+
 @pytest.mark.parametrize("nq,nkv,d,page,window", [
     (4, 2, 128, 16, None), (6, 1, 64, 16, None), (4, 4, 128, 32, 200), (3, 1, 64, 64, 129), (2, 1, 96, 16, 300)])
 def test_attention_long_portions(cuda_kernels, monkeypatch, nq, nkv, d, page, window):
