@@ -544,8 +544,8 @@ attn_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kv_pool,
 // padding: ldmatrix reads the swizzled tiles without bank conflicts.  Keys of a tile
 // beyond the token's range get zero weight; what the page holds there is finite (the
 // pool starts as zeros and only finite values are ever written to it).
-template <int D, int STAGES>
-__global__ void __launch_bounds__(128)
+template <int D, int STAGES, int WARPS>
+__global__ void __launch_bounds__(WARPS * 32)
 attn_decode_tma_kernel(const __grid_constant__ CUtensorMap pool_map, const bf16* __restrict__ q,
                        const int* __restrict__ block_table, const int4* __restrict__ decode_meta,
                        bf16* __restrict__ out, int nq, int nkv, int page_size, int page_shift, int max_blocks,
@@ -555,8 +555,9 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap pool_map, const bf16*
   constexpr int HALVES = D / 64;
   constexpr int TILE_BYTES = 16 * D * 2;                // one K or V tile: HALVES boxes of 2 KB
   constexpr int STAGE_BYTES = 2 * TILE_BYTES;
-  constexpr int STAGE_BYTES_ALL = 4 * STAGES * STAGE_BYTES;
-  constexpr int MERGE_BYTES = (4 * 16 * D + 2 * 4 * 16) * 4;
+  constexpr int STAGE_BYTES_ALL = WARPS * STAGES * STAGE_BYTES;
+  constexpr int THREADS = WARPS * 32;
+  constexpr int MERGE_BYTES = (WARPS * 16 * D + 2 * WARPS * 16) * 4;
   constexpr int FIN_BYTES = (16 * D + 32) * 4;
   constexpr int WORK_BYTES = STAGE_BYTES_ALL > MERGE_BYTES + FIN_BYTES ? STAGE_BYTES_ALL : MERGE_BYTES + FIN_BYTES;
   extern __shared__ unsigned char smem_dyn[];
@@ -566,14 +567,14 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap pool_map, const bf16*
   float* fin_m = fin_o + 16 * D;
   float* fin_l = fin_m + 16;
   bf16* q_s = reinterpret_cast<bf16*>(stage_base + WORK_BYTES);           // [16][LDS]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(q_s + 16 * LDS);          // [4 warps][STAGES]
-  int* tbl_s = reinterpret_cast<int*>(bars + 4 * STAGES);                // [tbl_cap]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(q_s + 16 * LDS);          // [warps][STAGES]
+  int* tbl_s = reinterpret_cast<int*>(bars + WARPS * STAGES);                // [tbl_cap]
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int item = blockIdx.x, g = blockIdx.y, split = blockIdx.z, num_splits = gridDim.z;
   const int G = nq / nkv;
   if (tid == 0) {
-    for (int i = 0; i < 4 * STAGES; ++i) mbar_init(smem_addr(bars + i), 1);
+    for (int i = 0; i < WARPS * STAGES; ++i) mbar_init(smem_addr(bars + i), 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   // The step's metadata, the block table and every key but the token's own were written before this
@@ -589,13 +590,13 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap pool_map, const bf16*
   const int kfirst = window > 0 ? max(0, pos - window + 1) : 0;
   const int kstart = kfirst & ~15;                      // tiles start on multiples of 16 so that one lies in one page
   const int kend = pos + 1;
-  const int per_split = (((kend - kstart + num_splits - 1) / num_splits) + 63) / 64 * 64;
+  const int per_split = (((kend - kstart + num_splits - 1) / num_splits) + WARPS * 16 - 1) / (WARPS * 16) * (WARPS * 16);
   const int k0 = kstart + split * per_split;
   const int k1 = min(kend, k0 + per_split);
   if (k0 < k1) {
     const int b0 = k0 >> page_shift, b1 = (k1 - 1) >> page_shift;
     if (b1 - b0 + 1 <= tbl_cap) {
-      for (int i = tid; i <= b1 - b0; i += 128) tbl_s[i] = table_g[b0 + i];
+      for (int i = tid; i <= b1 - b0; i += THREADS) tbl_s[i] = table_g[b0 + i];
       table = tbl_s;
       blk_base = b0;
     }
@@ -624,7 +625,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap pool_map, const bf16*
   };
 
   const int first_base = k0 + warp * 16;
-  const int stride = 64;
+  const int stride = WARPS * 16;
   if (lane == 0) {
 #pragma unroll
     for (int s = 0; s < STAGES - 1; ++s) {
@@ -640,7 +641,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap pool_map, const bf16*
       if (base < k1 && base + 16 > pos) issue_tile(base, s);
     }
   }
-  for (int i = tid; i < 16 * CPR; i += 128) {
+  for (int i = tid; i < 16 * CPR; i += THREADS) {
     const int row = i / CPR, c = i % CPR;
     uint4 v = make_uint4(0u, 0u, 0u, 0u);
     if (row < G) v = *reinterpret_cast<const uint4*>(q + ((size_t)t * nq + g * G + row) * D + c * 8);
@@ -750,8 +751,8 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap pool_map, const bf16*
   // ---- merge the four warps in shared memory (the staging buffers are free now)
   __syncthreads();
   float* c_o = reinterpret_cast<float*>(stage_base);          // [4][16][D]
-  float* c_m = c_o + 4 * 16 * D;
-  float* c_l = c_m + 4 * 16;
+  float* c_m = c_o + WARPS * 16 * D;
+  float* c_l = c_m + WARPS * 16;
   {
     const int r_lo = lane >> 2, r_hi = r_lo + 8;
 #pragma unroll
@@ -770,15 +771,15 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap pool_map, const bf16*
     }
   }
   __syncthreads();
-  for (int idx = tid; idx < G * D; idx += 128) {
+  for (int idx = tid; idx < G * D; idx += THREADS) {
     const int row = idx / D, dim = idx % D;
     float M = -INFINITY;
 #pragma unroll
-    for (int w = 0; w < 4; ++w) M = fmaxf(M, c_m[w * 16 + row]);
+    for (int w = 0; w < WARPS; ++w) M = fmaxf(M, c_m[w * 16 + row]);
     float O = 0.0f, L = 0.0f;
     if (M != -INFINITY) {
 #pragma unroll
-      for (int w = 0; w < 4; ++w) {
+      for (int w = 0; w < WARPS; ++w) {
         const float f = exp2f(c_m[w * 16 + row] - M);
         O += f * c_o[(w * 16 + row) * D + dim];
         L += f * c_l[w * 16 + row];
@@ -798,7 +799,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap pool_map, const bf16*
   cg::cluster_group cluster = cg::this_cluster();
   cluster.sync();
   const int DS = D / num_splits;
-  for (int idx = tid; idx < G * DS; idx += 128) {
+  for (int idx = tid; idx < G * DS; idx += THREADS) {
     const int row = idx / DS, dim = split * DS + idx % DS;
     float ms[16], ls[16], os[16];
 #pragma unroll
@@ -829,22 +830,23 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap pool_map, const bf16*
   cluster.sync();
 }
 
-template <int D, int STAGES>
+template <int D, int STAGES, int WARPS>
 int launch_decode_tma_stages(const CUtensorMap& pool_map, const bf16* q, const int* block_table, const int4* decode_meta,
                              bf16* out, int num_items, int nq, int nkv, int page_size, int page_shift, int max_blocks,
                              int num_pages, int window, float scale_log2, int num_splits, int max_keys, int* error_flag,
                              cudaStream_t stream) {
-  constexpr int stage_bytes = 4 * STAGES * 2 * 16 * D * 2;
-  constexpr int merge_bytes = (4 * 16 * D + 2 * 4 * 16) * 4;
+  constexpr int stage_bytes = WARPS * STAGES * 2 * 16 * D * 2;
+  constexpr int merge_bytes = (WARPS * 16 * D + 2 * WARPS * 16) * 4;
   constexpr int fin_bytes = (16 * D + 32) * 4;
   constexpr int work_bytes = stage_bytes > merge_bytes + fin_bytes ? stage_bytes : merge_bytes + fin_bytes;
-  const int per_split = (((max_keys + 16 + num_splits - 1) / num_splits) + 63) / 64 * 64;
+  constexpr int keys_round = WARPS * 16;
+  const int per_split = (((max_keys + 16 + num_splits - 1) / num_splits) + keys_round - 1) / keys_round * keys_round;
   int tbl_cap = per_split / page_size + 2;
   if (tbl_cap > 8192) tbl_cap = 0;
-  const int smem = 1024 + work_bytes + 16 * (D + 8) * 2 + 4 * STAGES * 8 + tbl_cap * 4;
+  const int smem = 1024 + work_bytes + 16 * (D + 8) * 2 + WARPS * STAGES * 8 + tbl_cap * 4;
   static int configured = 0;
   if (smem > configured) {
-    cudaError_t e = cudaFuncSetAttribute(attn_decode_tma_kernel<D, STAGES>,
+    cudaError_t e = cudaFuncSetAttribute(attn_decode_tma_kernel<D, STAGES, WARPS>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return (int)e;
     configured = smem;
@@ -852,35 +854,35 @@ int launch_decode_tma_stages(const CUtensorMap& pool_map, const bf16* q, const i
   if (num_splits > 8) {                                   // a cluster of 16 is beyond the portable size
     static bool allowed = false;
     if (!allowed) {
-      cudaError_t e = cudaFuncSetAttribute(attn_decode_tma_kernel<D, STAGES>,
+      cudaError_t e = cudaFuncSetAttribute(attn_decode_tma_kernel<D, STAGES, WARPS>,
                                            cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
       if (e != cudaSuccess) return (int)e;
       allowed = true;
     }
   }
-  return launch_pdl(attn_decode_tma_kernel<D, STAGES>, dim3(num_items, nkv, num_splits), dim3(128), (size_t)smem, stream,
-                    num_splits, pool_map, q, block_table, decode_meta, out, nq, nkv, page_size, page_shift, max_blocks,
-                    num_pages, window, scale_log2, tbl_cap, error_flag);
+  return launch_pdl(attn_decode_tma_kernel<D, STAGES, WARPS>, dim3(num_items, nkv, num_splits), dim3(WARPS * 32),
+                    (size_t)smem, stream, num_splits, pool_map, q, block_table, decode_meta, out, nq, nkv, page_size,
+                    page_shift, max_blocks, num_pages, window, scale_log2, tbl_cap, error_flag);
 }
 
-// Three 16-key tiles in flight a warp (96 KB a block at head size 128) feed the HBM when two blocks sit on every
-// SM.  A grid of at most one block per SM with long key ranges (one or two tokens at tens of thousands of keys) is
-// bound by what a block keeps in flight instead: it gets rings twice as deep.
+// Four warps with three 16-key tiles in flight each (96 KB a block at head size 128) feed the HBM when two blocks
+// sit on every SM.  A grid that leaves at least half the SMs empty (one or two decoded tokens) is bound by the pace
+// of a warp's tile loop and by what a block has in flight: it runs with eight warps a block (a decode step of the
+// 7B shape at batch 1: 2.75 -> 2.68 ms at 4,096 keys, 3.39 -> 3.07 ms at 32,768).  With more blocks than that the
+// larger blocks no longer all find room at once, clusters of 16 in particular (batch 2 at 32,768 keys: 3.46 -> 3.68 ms).
 template <int D>
 int launch_decode_tma(const CUtensorMap& pool_map, const bf16* q, const int* block_table, const int4* decode_meta,
                       bf16* out, int num_items, int nq, int nkv, int page_size, int page_shift, int max_blocks,
                       int num_pages, int window, float scale_log2, int num_splits, int max_keys, int* error_flag,
                       cudaStream_t stream) {
-  constexpr int BASE = D <= 128 ? 3 : 2;
+  constexpr int STAGES = D <= 128 ? 3 : 2;
   const long long blocks = (long long)num_items * nkv * num_splits;
-  const int keys_per_warp = max_keys / (num_splits > 0 ? num_splits : 1) / 4;
-  if (D <= 128 && blocks <= 148 && keys_per_warp >= 16 * 4 * BASE)
-    return launch_decode_tma_stages<D, 2 * BASE>(pool_map, q, block_table, decode_meta, out, num_items, nq, nkv, page_size,
-                                                 page_shift, max_blocks, num_pages, window, scale_log2, num_splits, max_keys,
-                                                 error_flag, stream);
-  return launch_decode_tma_stages<D, BASE>(pool_map, q, block_table, decode_meta, out, num_items, nq, nkv, page_size,
-                                           page_shift, max_blocks, num_pages, window, scale_log2, num_splits, max_keys,
-                                           error_flag, stream);
+  const int keys_per_block = max_keys / (num_splits > 0 ? num_splits : 1);
+#define ARGS pool_map, q, block_table, decode_meta, out, num_items, nq, nkv, page_size, page_shift, max_blocks, num_pages, \
+             window, scale_log2, num_splits, max_keys, error_flag, stream
+  if (D <= 128 && blocks <= 74 && keys_per_block >= 8 * 16) return launch_decode_tma_stages<D, STAGES, 8>(ARGS);
+  return launch_decode_tma_stages<D, STAGES, 4>(ARGS);
+#undef ARGS
 }
 
 template <int D>
