@@ -866,10 +866,11 @@ int launch_decode_tma_stages(const CUtensorMap& pool_map, const bf16* q, const i
 }
 
 // Four warps with three 16-key tiles in flight each (96 KB a block at head size 128) feed the HBM when two blocks
-// sit on every SM.  A grid that leaves at least half the SMs empty (one or two decoded tokens) is bound by the pace
+// sit on every SM.  A grid that leaves a third of the SMs empty (one to three decoded tokens) is bound by the pace
 // of a warp's tile loop and by what a block has in flight: it runs with eight warps a block (a decode step of the
-// 7B shape at batch 1: 2.75 -> 2.68 ms at 4,096 keys, 3.39 -> 3.07 ms at 32,768).  With more blocks than that the
-// larger blocks no longer all find room at once, clusters of 16 in particular (batch 2 at 32,768 keys: 3.46 -> 3.68 ms).
+// 7B shape at batch 1, 64 blocks: 2.75 -> 2.68 ms at 4,096 keys, 3.39 -> 3.07 ms at 32,768; batch 3, 96 blocks:
+// 2.89 -> 2.80 and 4.20 -> 3.53 ms).  From 128 blocks on the larger blocks no longer all find room at once
+// (batch 2 with clusters of 16 at 32,768 keys: 3.46 -> 3.68 ms; batch 4: 4.25 -> 4.55 ms).
 template <int D>
 int launch_decode_tma(const CUtensorMap& pool_map, const bf16* q, const int* block_table, const int4* decode_meta,
                       bf16* out, int num_items, int nq, int nkv, int page_size, int page_shift, int max_blocks,
@@ -880,7 +881,7 @@ int launch_decode_tma(const CUtensorMap& pool_map, const bf16* q, const int* blo
   const int keys_per_block = max_keys / (num_splits > 0 ? num_splits : 1);
 #define ARGS pool_map, q, block_table, decode_meta, out, num_items, nq, nkv, page_size, page_shift, max_blocks, num_pages, \
              window, scale_log2, num_splits, max_keys, error_flag, stream
-  if (D <= 128 && blocks <= 74 && keys_per_block >= 8 * 16) return launch_decode_tma_stages<D, STAGES, 8>(ARGS);
+  if (D <= 128 && blocks <= 104 && keys_per_block >= 8 * 16) return launch_decode_tma_stages<D, STAGES, 8>(ARGS);
   return launch_decode_tma_stages<D, STAGES, 4>(ARGS);
 #undef ARGS
 }
