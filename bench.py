@@ -548,11 +548,11 @@ def main() -> int:
     if not args.no_points:
         k = min(steps, 20)
         for b in (1, 64):
-            r = time_decode(engine, cfg, b, k, 5, repeats=2, e2e=False)
+            r = time_decode(engine, cfg, b, k, 5, repeats=5, e2e=False)
             points[f"decode_b{b}"] = round(b * 1000.0 / r["dev_ms"], 1)
         window = [value]
         for ctx in (2048, 3072):
-            r = time_decode(engine, cfg, args.batch, k, 5, repeats=2, context=ctx, e2e=False)
+            r = time_decode(engine, cfg, args.batch, k, 5, repeats=4, context=ctx, e2e=False)
             window.append(args.batch * 1000.0 / r["dev_ms"])
             if ctx == 2048:
                 points[f"decode_b{args.batch}_ctx2048"] = round(window[-1], 1)
