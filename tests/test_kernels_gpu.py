@@ -93,7 +93,7 @@ def test_gemm_bfloat16(cuda_kernels, M, N, K, out_dtype):
     close(cuda_kernels.linear_generic(a, w, out_dtype=out_dtype), want, atol=1e-4 * math.sqrt(K), rtol=rtol)
 
 
-@pytest.mark.parametrize("M,N,K", [(1, 128, 64), (8, 256, 512), (17, 1000, 200), (33, 300, 328), (64, 3584, 1024),
+@pytest.mark.parametrize("M,N,K", [(1, 128, 64), (3, 80, 128), (8, 256, 512), (17, 1000, 200), (33, 300, 328), (64, 3584, 1024),
                                    (100, 130, 72), (128, 520, 4104), (5, 4608, 3584), (129, 264, 520), (200, 1000, 328),
                                    (256, 384, 4104)])
 def test_gemm_tcgen05_few_rows(cuda_kernels, monkeypatch, M, N, K):
