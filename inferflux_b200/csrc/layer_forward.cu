@@ -7,7 +7,7 @@
 // The reference's counterpart is the layer loop of LlamaForwardTyped<T>::Forward / BatchForwardDevice
 // (runtime/backends/cuda/native/transformer_forward.cu:1792-2600, 3100-3900), which is native too.
 //
-// Nothing here knows a model: the caller (CudaKernels.fused_block) hands in the sizes and constants of the
+// Nothing here knows a model: the caller (CudaKernels.fused_prenorm_layer) hands in the sizes and constants of the
 // layer's parts.  Temporaries live in a workspace the caller owns; the layer's last delta (the down
 // projection, not yet added to the residual stream) is left in one of two regions of it, alternating by
 // layer, for whatever normalises next.
@@ -92,6 +92,8 @@ struct Arena {
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
+// The routing rules below restate those of ops.py; tests/test_native_layer_gpu.py holds the two paths to each
+// other bit for bit, so a rule changed in one place only shows at once.
 // K slices of a few-rows product, as CudaKernels.linear chooses them.
 inline int skinny_splits(int T, int N, int K) {
   const int tiles = (N + 127) / 128, kblocks = (K + 63) / 64;
