@@ -162,8 +162,9 @@ def test_command_line_streams_the_tokens_it_reports(model_dirs):
 def test_many_requests_with_every_kind_of_sampling_twice(model_dirs, tiny_configs):
     """Sixty requests of random lengths and sampling settings (greedy, temperature, top-k, top-p, min-p,
     penalties, stop tokens) through a pool so small that requests are preempted, with overlapped steps:
-    every request finishes, every page comes back, a second run draws the same tokens, and the greedy
-    requests' tokens are the best ones under the plain implementation's logits."""
+    every request finishes, every page comes back, a second run draws the same tokens, so does a run whose
+    layers are launched part by part, and the greedy requests' tokens are the best ones under the plain
+    implementation's logits."""
     import random
     from inferflux_b200 import Engine, SamplingParams
     cfg, page = tiny_configs["E"]
@@ -181,9 +182,10 @@ def test_many_requests_with_every_kind_of_sampling_twice(model_dirs, tiny_config
               SamplingParams(temperature=0.0, presence_penalty=0.5)][kind]
         jobs.append((prompt, sp, rng.choice([1, 3, 12, 30]), rng.randrange(cfg.vocab_size) if i % 4 == 0 else None))
 
-    def run():
+    def run(native_layers=True):
         eng = Engine(d, dtype="bfloat16", kv_page_size=page, kv_num_pages=40, kv_max_batch=12, kv_max_seq=256,
                      max_batch_size=12, max_batch_tokens=96, chunked_prefill_tokens=48)
+        eng.kernels.native_layers = native_layers
         ids = [eng.add_request(p, sp, max_tokens=m, eos_token_id=eos) for p, sp, m, eos in jobs]
         done, guard = {}, 0
         while eng.has_unfinished():
@@ -200,6 +202,10 @@ def test_many_requests_with_every_kind_of_sampling_twice(model_dirs, tiny_config
     first, preemptions = run()
     second, _ = run()
     assert first == second
+    # the same with every kernel launched by its part instead of a layer at a time from native code: the logits
+    # are the same bits, so every request draws the same tokens
+    third, _ = run(native_layers=False)
+    assert first == third
     # against the oracle: what the greedy requests chose is the best token of the plain logits of their
     # own sequence, within bfloat16 rounding (a wrong page or a stale key after a preemption would show)
     raw, W = plain_qwen2.load_model_dir(d)
